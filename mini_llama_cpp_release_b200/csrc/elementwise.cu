@@ -13,14 +13,14 @@ namespace mlc {
 
 // ------------------------------------------------------------------ embedding
 template <typename T>
-__global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids, int d,
+__global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids, int d, float scale,
                              float* __restrict__ out) {
     grid_launch_dependents();
     grid_dependency_wait();
     const int n = blockIdx.x;
     const T* row = table + (long long)ids[n] * d;
     float* o = out + (long long)n * d;
-    for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = to_float(row[i]);
+    for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = to_float(row[i]) * scale;
 }
 
 // ------------------------------------------------------------------ residual add + RMSNorm
@@ -527,16 +527,17 @@ static inline int norm_threads(int d, int n) {
 
 using namespace mlc;
 
-extern "C" int mlc_embed(const void* table, int table_dtype, const int* ids, int n, int d, float* out,
+// out[t] = table[ids[t]] · scale (a scale of one changes nothing, bit for bit)
+extern "C" int mlc_embed(const void* table, int table_dtype, const int* ids, int n, int d, float scale, float* out,
                          void* stream) {
     if (n <= 0) return 0;
     if (d <= 0) return MLC_ERR_BAD_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
     cudaError_t e;
     if (table_dtype == MLC_DTYPE_F32)
-        e = launch_pdl(embed_kernel<float>, dim3(n), dim3(norm_threads(d, n)), 0, s, (const float*)table, ids, d, out);
+        e = launch_pdl(embed_kernel<float>, dim3(n), dim3(norm_threads(d, n)), 0, s, (const float*)table, ids, d, scale, out);
     else if (table_dtype == MLC_DTYPE_BF16)
-        e = launch_pdl(embed_kernel<bf16>, dim3(n), dim3(norm_threads(d, n)), 0, s, (const bf16*)table, ids, d, out);
+        e = launch_pdl(embed_kernel<bf16>, dim3(n), dim3(norm_threads(d, n)), 0, s, (const bf16*)table, ids, d, scale, out);
     else
         return MLC_ERR_BAD_DTYPE;
     return e == cudaSuccess ? 0 : (int)e;

@@ -31,7 +31,16 @@ struct RowsArgs {
     // n_out rows starting at row e * n_out of W.  tile_group [m_tiles]: the tile's group, negative: the tile is skipped.
     // The table comes from a kernel before this one, so nothing is asked for ahead of the wait for that kernel.
     const int* tile_group;
+    // STORE only: an activation applied to the product before it is stored (0 none, 1 silu, 2 gelu with erf, 3 gelu with
+    // the tanh approximation), in float32
+    int act;
 };
+
+__device__ __forceinline__ float rows_activation(float z, int act) {
+    if (act == 1) return z / (1.0f + expf(-z));
+    if (act == 2) return 0.5f * z * (1.0f + erff(z * 0.70710678118654752440f));
+    return 0.5f * z * (1.0f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
+}
 
 constexpr int R_BM = 128;
 constexpr int R_BK = 64;
@@ -47,7 +56,14 @@ __device__ __forceinline__ unsigned pack2(float a, float b) {
 // per element and launch unless the K range is shared out over blocks); SILU_MUL: columns alternate gate_j, up_j
 // and gate·sigmoid(gate)·up goes to [token][n/2].
 template <int EPI>
-__device__ __forceinline__ void rows_epilogue_chunk(const RowsArgs& g, const float (&v)[32], int tok, int n, bool second) {
+__device__ __forceinline__ void rows_epilogue_chunk(const RowsArgs& g, const float (&vin)[32], int tok, int n, bool second) {
+    float v[32];
+#pragma unroll
+    for (int u = 0; u < 32; ++u) v[u] = vin[u];
+    if (EPI == R_EPI_STORE && g.act != 0) {
+#pragma unroll
+        for (int u = 0; u < 32; ++u) v[u] = rows_activation(v[u], g.act);
+    }
     if (EPI == R_EPI_STORE) {
         if (g.out_dtype == MLC_DTYPE_BF16) {
             uint4* dst = reinterpret_cast<uint4*>((bf16*)g.out + (long long)tok * g.n_out + n);

@@ -359,8 +359,9 @@ extern "C" int mlc_gemm_tcgen05_rows(const void* x, const void* w, void* out, in
 
 // The grouped form: x bfloat16 [n_rows][K], n_rows a multiple of 128, every tile of 128 rows belonging to one group;
 // w bfloat16 [n_groups * n_out][K], group e's matrix in rows e * n_out on; tile_group int32 [n_rows / 128] on the device
-// (negative: the tile holds no rows and is skipped).  Epilogues 0 (out [n_rows][n_out] float32 or bfloat16) and 1
-// (gate and up rows interleaved, out [n_rows][n_out / 2]).  Status codes as above.
+// (negative: the tile holds no rows and is skipped).  Epilogues 0 (out [n_rows][n_out] float32 or bfloat16), 1
+// (gate and up rows interleaved, out [n_rows][n_out / 2]) and 4, 5, 6 (as 0 with silu, gelu with erf, gelu with the tanh
+// approximation applied to the product before it is stored).  Status codes as above.
 extern "C" int mlc_gemm_tcgen05_rows_grouped(const void* x, const void* w, void* out, int out_dtype, int n_rows, int n_out, int K,
                                              int block_rows, int epilogue, int* status, int n_sms, const int* tile_group,
                                              int n_groups, void* stream) {
@@ -368,8 +369,12 @@ extern "C" int mlc_gemm_tcgen05_rows_grouped(const void* x, const void* w, void*
     if (K <= 0 || (K & 7) || (n_out & 15) || (n_rows % R_BM) || (((uintptr_t)x | (uintptr_t)w | (uintptr_t)out) & 15)) return MLC_ERR_BAD_SIZE;
     if (out_dtype != MLC_DTYPE_F32 && out_dtype != MLC_DTYPE_BF16) return MLC_ERR_BAD_DTYPE;
     if (status == nullptr || n_sms < 1 || tile_group == nullptr || n_groups < 1) return MLC_ERR_BAD_SIZE;
-    if (epilogue != R_EPI_STORE && epilogue != R_EPI_SILU_MUL) return MLC_ERR_UNSUPPORTED;
+    if (epilogue != R_EPI_STORE && epilogue != R_EPI_SILU_MUL && (epilogue < 4 || epilogue > 6)) return MLC_ERR_UNSUPPORTED;
     RowsArgs g{};
+    if (epilogue >= 4) {
+        g.act = epilogue - 3;
+        epilogue = R_EPI_STORE;
+    }
     g.out = out;
     g.out_dtype = out_dtype;
     g.n_out = n_out;

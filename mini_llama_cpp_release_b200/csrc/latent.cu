@@ -17,8 +17,12 @@ namespace mlc {
 // Cache row (kv head 0): [c · (rsqrt(mean c² + eps) · gain) | rotated key part | zeros up to D].
 // q_out [n][H][D]: entries [rank, rank + rot) get the rotated query part, [rank + rot, D) zeros; [0, rank) is left to
 // the projection that follows.  q_plain_out [n][H][dim] float32: the unrotated query parts, dense.
+// `qsrc` (row stride `q_stride`) holds the query heads at q_col; it may be `proj` itself or another matrix (queries that
+// come out of a product of their own, behind a query latent).  `interleaved`: the rotation pairs entry 2i with 2i + 1
+// instead of i with i + rot/2; the table is the same, [position][pair] (cos, sin).
 template <typename T>
-__global__ void latent_prepare_kernel(const float* __restrict__ proj, long long stride, int q_col, int kv_col,
+__global__ void latent_prepare_kernel(const float* __restrict__ proj, long long stride, const float* __restrict__ qsrc,
+                                      long long q_stride, int interleaved, int q_col, int kv_col,
                                       const float* __restrict__ gain, float eps, const int* __restrict__ positions,
                                       const int* __restrict__ tok_seq, const float2* __restrict__ rope, int rope_positions,
                                       int H, int dim, int rot, int rank, int D, T* __restrict__ q_out, int write_cache,
@@ -31,17 +35,18 @@ __global__ void latent_prepare_kernel(const float* __restrict__ proj, long long 
     const float2* cs = (rope != nullptr && half > 0) ? rope + (long long)min(p, rope_positions - 1) * half : nullptr;
     for (int head = warp; head < H + 1; head += n_warps) {
         if (head < H) {
-            const float* src = row + q_col + (long long)head * (dim + rot) + dim;
+            const float* src = qsrc + (long long)n * q_stride + q_col + (long long)head * (dim + rot) + dim;
             T* dst = q_out + ((long long)n * H + head) * D + rank;
             for (int i = lane; i < D - rank; i += 32) {
                 float v = 0.0f;
                 if (i < rot) {
                     v = src[i];
                     if (cs != nullptr) {
-                        const int j = i < half ? i : i - half;
-                        const float w = src[i < half ? i + half : i - half];
+                        const bool first = interleaved ? !(i & 1) : i < half;
+                        const int j = interleaved ? i >> 1 : (i < half ? i : i - half);
+                        const float w = src[interleaved ? i ^ 1 : (i < half ? i + half : i - half)];
                         const float2 t = cs[j];
-                        v = i < half ? v * t.x - w * t.y : v * t.x + w * t.y;
+                        v = first ? v * t.x - w * t.y : v * t.x + w * t.y;
                     }
                 }
                 dst[i] = from_float<T>(v);
@@ -61,10 +66,11 @@ __global__ void latent_prepare_kernel(const float* __restrict__ proj, long long 
                     const int k = i - rank;
                     v = src[i];
                     if (cs != nullptr) {
-                        const int j = k < half ? k : k - half;
-                        const float w = src[rank + (k < half ? k + half : k - half)];
+                        const bool first = interleaved ? !(k & 1) : k < half;
+                        const int j = interleaved ? k >> 1 : (k < half ? k : k - half);
+                        const float w = src[rank + (interleaved ? k ^ 1 : (k < half ? k + half : k - half))];
                         const float2 t = cs[j];
-                        v = k < half ? v * t.x - w * t.y : v * t.x + w * t.y;
+                        v = first ? v * t.x - w * t.y : v * t.x + w * t.y;
                     }
                 }
                 dst[i] = from_float<T>(v);
@@ -132,7 +138,8 @@ head_project_kernel(const TI* __restrict__ in, long long in_st, long long in_sh,
 
 using namespace mlc;
 
-extern "C" int mlc_latent_prepare(const float* proj, long long stride, int q_col, int kv_col, const float* gain, float eps,
+extern "C" int mlc_latent_prepare(const float* proj, long long stride, const float* qsrc, long long q_stride, int interleaved,
+                                  int q_col, int kv_col, const float* gain, float eps,
                                   const int* positions, const int* tok_seq, const void* rope_table, int rope_positions, int n,
                                   int H, int dim, int rot, int rank, int D, void* q_out, int dtype, int write_cache,
                                   void* k_pool, const int* page_table, long long entry_offset, int pages_per_seq,
@@ -143,11 +150,11 @@ extern "C" int mlc_latent_prepare(const float* proj, long long stride, int q_col
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = 32 * (H + 1 < 8 ? H + 1 : 8);
     if (dtype == MLC_DTYPE_F32)
-        latent_prepare_kernel<float><<<n, threads, 0, s>>>(proj, stride, q_col, kv_col, gain, eps, positions, tok_seq,
+        latent_prepare_kernel<float><<<n, threads, 0, s>>>(proj, stride, qsrc, q_stride, interleaved, q_col, kv_col, gain, eps, positions, tok_seq,
                                                            (const float2*)rope_table, rope_positions, H, dim, rot, rank, D,
                                                            (float*)q_out, write_cache, c);
     else if (dtype == MLC_DTYPE_BF16)
-        latent_prepare_kernel<bf16><<<n, threads, 0, s>>>(proj, stride, q_col, kv_col, gain, eps, positions, tok_seq,
+        latent_prepare_kernel<bf16><<<n, threads, 0, s>>>(proj, stride, qsrc, q_stride, interleaved, q_col, kv_col, gain, eps, positions, tok_seq,
                                                           (const float2*)rope_table, rope_positions, H, dim, rot, rank, D,
                                                           (bf16*)q_out, write_cache, c);
     else

@@ -27,8 +27,10 @@ constexpr int GLA_THREADS = 64;    // 8 pairs of columns x 8 groups of rows
 constexpr int GLA_V_LOADS = GLA_CHUNK * GLA_COLS / GLA_THREADS;
 
 struct GlaArgs {
-    const float* proj;          // rows of the input product
-    long long proj_stride;
+    const float* qk;            // rows that hold q (at q_col) and k (at k_col)
+    long long qk_stride;
+    const float* vsrc;          // rows that hold v (at v_col); may be the same matrix
+    long long v_stride;
     int q_col, k_col, v_col;
     const float* decay;         // [n][H*dim] decays
     float q_scale;
@@ -48,6 +50,31 @@ __global__ void gla_decay_kernel(float* __restrict__ z, const float* __restrict_
     if (idx >= total) return;
     const float x = z[idx] + (bias != nullptr ? bias[idx % width] : 0.0f);
     z[idx] = expf((fminf(x, 0.0f) - log1pf(expf(-fabsf(x)))) * inv_tau);
+}
+
+// The forget-gate form (the HGRN2 design): the
+// decay of a key channel is a forget gate with a lower bound, and what is written through that channel is its complement:
+//   f = l + (1 - l) · sigmoid(z_f + b),   S_t = diag(f_t) S_{t-1} + (1 - f_t) v_tᵀ,   o_t = S_tᵀ silu(z_q)
+// which is the walk above with decay f, key 1 - f, query silu(z_q) and no scale.  This kernel makes the three from the
+// rows of the input product: qk [n][2·HD] = [silu(z_q) | (1 - l) · sigmoid(-(z_f + b))], decay [n][HD] = f.  The key is formed as
+// (1 - l)(1 - sigmoid), not as 1 - f: a gate close to one would leave 1 - f with few digits.
+__global__ void forget_gates_kernel(const float* __restrict__ proj, long long stride, int q_col, int f_col,
+                                    const float* __restrict__ f_bias, const float* __restrict__ lower, long long total, int width,
+                                    float* __restrict__ qk, float* __restrict__ decay) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const long long t = idx / width;
+    const int c = (int)(idx - t * width);
+    const float* row = proj + t * stride;
+    const float zq = row[q_col + c];
+    const float zf = row[f_col + c] + (f_bias != nullptr ? f_bias[c] : 0.0f);
+    const float l = lower != nullptr ? lower[c] : 0.0f;
+    const float e = expf(-fabsf(zf));                 // sigmoid(zf) and sigmoid(-zf) without overflow
+    const float big = 1.0f / (1.0f + e), small = e / (1.0f + e);
+    const float sig = zf >= 0.0f ? big : small, co = zf >= 0.0f ? small : big;
+    qk[t * 2 * width + c] = zq / (1.0f + expf(-zq));
+    qk[t * 2 * width + width + c] = (1.0f - l) * co;
+    decay[idx] = l + (1.0f - l) * sig;
 }
 
 // ROWS floats from 8- or 16-byte aligned shared memory
@@ -102,7 +129,7 @@ gla_walk_kernel(GlaArgs a) {
             rq[u] = rk[u] = 0.0f;
             ra[u] = 1.0f;                             // no token, or no such channel: a decay of one, q and k zero
             if (tt < n_here && row0 + d < dim) {
-                const float* row = a.proj + (long long)(c0 + tt) * a.proj_stride + head * dim + row0 + d;
+                const float* row = a.qk + (long long)(c0 + tt) * a.qk_stride + head * dim + row0 + d;
                 rq[u] = row[a.q_col];
                 rk[u] = row[a.k_col];
                 ra[u] = a.decay[(long long)(c0 + tt) * a.H * dim + head * dim + row0 + d];
@@ -112,7 +139,7 @@ gla_walk_kernel(GlaArgs a) {
         for (int u = 0; u < GLA_V_LOADS; ++u) {
             const int idx = tid + u * GLA_THREADS;
             const int tt = idx / GLA_COLS, cc = idx % GLA_COLS;
-            rv[u] = (tt < n_here && col0 + cc < vdim) ? a.proj[(long long)(c0 + tt) * a.proj_stride + a.v_col + head * vdim + col0 + cc] : 0.0f;
+            rv[u] = (tt < n_here && col0 + cc < vdim) ? a.vsrc[(long long)(c0 + tt) * a.v_stride + a.v_col + head * vdim + col0 + cc] : 0.0f;
         }
     };
     if (t0 < t1) fetch(t0);
@@ -211,6 +238,25 @@ extern "C" int mlc_gla_rows(int n_seqs, int H, int dim, int vdim, int n_sms) {
     return rows;
 }
 
+// The walk alone, over decays that are already made: q and k (H x dim each) in the float32 rows `qk`, v (H x vdim) in the rows
+// `v` (the same matrix or another), decay float32 [n][H*dim].
+static int gla_walk(const float* qk, long long qk_stride, int q_col, int k_col, const float* v, long long v_stride, int v_col,
+                    const float* decay, float q_scale, float* state, long long state_stride, const int* slots,
+                    const int* cu_seqlens, int n_seqs, int n_tokens, int H, int dim, int vdim, int rows, float* out,
+                    cudaStream_t s) {
+    if (H <= 0 || dim <= 0 || dim > 256 || vdim <= 0 || n_seqs > 65535) return MLC_ERR_BAD_SIZE;
+    if (rows != 2 && rows != 4 && rows != 8 && rows != 16 && rows != 32) return MLC_ERR_BAD_SIZE;
+    const int col_slabs = (vdim + GLA_COLS - 1) / GLA_COLS, row_slabs = (dim + 8 * rows - 1) / (8 * rows);
+    GlaArgs a{qk, qk_stride, v, v_stride, q_col, k_col, v_col, decay, q_scale, state, state_stride,
+              slots, cu_seqlens, out, (long long)n_tokens * H * vdim, H, dim, vdim, col_slabs};
+    const dim3 grid(H, n_seqs, col_slabs * row_slabs);
+    if (rows == 2) return launch_gla<2>(a, grid, s);
+    if (rows == 4) return launch_gla<4>(a, grid, s);
+    if (rows == 8) return launch_gla<8>(a, grid, s);
+    if (rows == 16) return launch_gla<16>(a, grid, s);
+    return launch_gla<32>(a, grid, s);
+}
+
 // proj: float32 rows (stride proj_stride) holding q (H x dim) at q_col, k (H x dim) at k_col, v (H x vdim) at v_col.
 // z: float32 [n][H*dim] decay logits (overwritten with the decays), z_bias [H*dim] or null.  state: float32, a slot's row
 // holds H*vdim*dim floats.  rows: what mlc_gla_rows gave.  out: float32 [ceil(dim / (8 * rows))][n][H*vdim], partial
@@ -226,13 +272,25 @@ extern "C" int mlc_gla(const float* proj, long long proj_stride, int q_col, int 
     const long long total = (long long)n_tokens * H * dim;
     gla_decay_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(z, z_bias, total, H * dim, 1.0f / tau);
     MLC_LAUNCH_CHECK();
-    const int col_slabs = (vdim + GLA_COLS - 1) / GLA_COLS, row_slabs = (dim + 8 * rows - 1) / (8 * rows);
-    GlaArgs a{proj, proj_stride, q_col, k_col, v_col, z, 1.0f / sqrtf((float)dim), state, state_stride,
-              slots, cu_seqlens, out, (long long)n_tokens * H * vdim, H, dim, vdim, col_slabs};
-    const dim3 grid(H, n_seqs, col_slabs * row_slabs);
-    if (rows == 2) return launch_gla<2>(a, grid, s);
-    if (rows == 4) return launch_gla<4>(a, grid, s);
-    if (rows == 8) return launch_gla<8>(a, grid, s);
-    if (rows == 16) return launch_gla<16>(a, grid, s);
-    return launch_gla<32>(a, grid, s);
+    return gla_walk(proj, proj_stride, q_col, k_col, proj, proj_stride, v_col, z, 1.0f / sqrtf((float)dim), state, state_stride,
+                    slots, cu_seqlens, n_seqs, n_tokens, H, dim, vdim, rows, out, s);
+}
+
+// The forget-gate form: proj float32 rows holding the query logits (H x dim) at q_col, the gate logits (H x dim) at f_col
+// and v (H x vdim) at v_col; f_bias, lower [H*dim] or null (no bias; a lower bound of zero).  qk float32 [n][2*H*dim] and
+// decay float32 [n][H*dim] are scratch that this call fills.  state, rows, out as in mlc_gla.
+extern "C" int mlc_forget_gate_attention(const float* proj, long long proj_stride, int q_col, int f_col, int v_col,
+                                         const float* f_bias, const float* lower, float* qk, float* decay, float* state,
+                                         long long state_stride, const int* slots, const int* cu_seqlens, int n_seqs,
+                                         int n_tokens, int H, int dim, int vdim, int rows, float* out, void* stream) {
+    if (n_seqs <= 0 || n_tokens <= 0) return 0;
+    if (H <= 0 || dim <= 0 || dim > 256 || vdim <= 0 || n_seqs > 65535) return MLC_ERR_BAD_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int width = H * dim;
+    const long long total = (long long)n_tokens * width;
+    forget_gates_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(proj, proj_stride, q_col, f_col, f_bias, lower, total,
+                                                                         width, qk, decay);
+    MLC_LAUNCH_CHECK();
+    return gla_walk(qk, 2LL * width, 0, width, proj, proj_stride, v_col, decay, 1.0f, state, state_stride, slots, cu_seqlens,
+                    n_seqs, n_tokens, H, dim, vdim, rows, out, s);
 }

@@ -22,6 +22,39 @@ constexpr int ROUTE_MAX_PER_LANE = 8;          // E <= 256
 // x · wᵀ + bias in float32 (w float32 [E][K]): eight experts at a time, every thread a strided share of K, partial sums
 // added within warps and then across them in a fixed order.  Without `w`, `x` holds the logits themselves, float32 [n][E].
 // Warp 0 then chooses: lane l keeps logits l, l + 32, ...
+// Router logits of token t into shared `logit[E]`: x · wᵀ + bias in float32 (w float32 [E][K]), eight experts at a time,
+// every thread a strided share of K, partial sums added within warps and then across them in a fixed order.  All 128
+// threads of the block call it.
+template <typename TX>
+__device__ __forceinline__ void route_logits(const TX* __restrict__ x, const float* __restrict__ w, const float* __restrict__ bias,
+                                             int t, int E, int K, float (*part)[8], float* logit) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const TX* row = x + (long long)t * K;
+    for (int e0 = 0; e0 < E; e0 += 8) {
+        float acc[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
+#pragma unroll 4
+        for (int k = threadIdx.x; k < K; k += 128) {
+            const float xv = to_float(row[k]);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] = fmaf(xv, __ldg(w + (long long)min(e0 + j, E - 1) * K + k), acc[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float v = warp_sum(acc[j]);
+            if (lane == 0) part[warp][j] = v;
+        }
+        __syncthreads();
+        if (threadIdx.x < 8 && e0 + threadIdx.x < E) {
+            const int e = e0 + threadIdx.x;
+            logit[e] = ((part[0][threadIdx.x] + part[1][threadIdx.x]) + (part[2][threadIdx.x] + part[3][threadIdx.x]))
+                       + (bias != nullptr ? bias[e] : 0.0f);
+        }
+        __syncthreads();
+    }
+}
+
 template <typename TX>
 __global__ void __launch_bounds__(128)
 moe_route_kernel(const TX* __restrict__ x, const float* __restrict__ w, const float* __restrict__ bias, int n,
@@ -30,32 +63,7 @@ moe_route_kernel(const TX* __restrict__ x, const float* __restrict__ w, const fl
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     __shared__ float part[4][8];
     __shared__ float logit[32 * ROUTE_MAX_PER_LANE];
-    if (w != nullptr) {
-        const TX* row = x + (long long)t * K;
-        for (int e0 = 0; e0 < E; e0 += 8) {
-            float acc[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
-#pragma unroll 4
-            for (int k = threadIdx.x; k < K; k += 128) {
-                const float xv = to_float(row[k]);
-#pragma unroll
-                for (int j = 0; j < 8; ++j) acc[j] = fmaf(xv, __ldg(w + (long long)min(e0 + j, E - 1) * K + k), acc[j]);
-            }
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const float v = warp_sum(acc[j]);
-                if (lane == 0) part[warp][j] = v;
-            }
-            __syncthreads();
-            if (threadIdx.x < 8 && e0 + threadIdx.x < E) {
-                const int e = e0 + threadIdx.x;
-                logit[e] = ((part[0][threadIdx.x] + part[1][threadIdx.x]) + (part[2][threadIdx.x] + part[3][threadIdx.x]))
-                           + (bias != nullptr ? bias[e] : 0.0f);
-            }
-            __syncthreads();
-        }
-    }
+    if (w != nullptr) route_logits<TX>(x, w, bias, t, E, K, part, logit);
     if (warp != 0) return;
     float z[ROUTE_MAX_PER_LANE];
 #pragma unroll
@@ -100,6 +108,126 @@ moe_route_kernel(const TX* __restrict__ x, const float* __restrict__ w, const fl
     if (lane < top) weights[(long long)t * top + lane] = p / sum;
 }
 
+// Routing by scores of all experts.  s = softmax(z) over all E router outputs; an expert is *chosen* by s + correction
+// (a stored per-expert term that steers the choice only) and *weighted* by s itself:
+//   groups   the E outputs form G equal groups of neighbours; a group's score is its largest choice score, and only
+//            experts of the `keep` best groups can be chosen (the others count as minus infinity);
+//   choice   the `top` largest remaining choice scores (the lower index wins a tie);
+//   weights  s of the chosen, divided by their sum + 1e-20, times `scale`.
+// The last E - n_real outputs belong to identity experts (no matrices: the token's input itself); they are chosen and
+// weighted like the others, and whoever sums the rows treats their ids apart.  A block of four warps per token forms the
+// logits, warp 0 chooses.
+template <typename TX>
+__global__ void __launch_bounds__(128)
+moe_route_scored_kernel(const TX* __restrict__ x, const float* __restrict__ w, const float* __restrict__ correction, int n,
+                        int E, int K, int top, int G, int keep, float scale, int* __restrict__ ids,
+                        float* __restrict__ weights) {
+    const int t = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    __shared__ float part[4][8];
+    __shared__ float logit[32 * ROUTE_MAX_PER_LANE];
+    __shared__ float prob[32 * ROUTE_MAX_PER_LANE];
+    __shared__ float gscore[32 * ROUTE_MAX_PER_LANE];
+    route_logits<TX>(x, w, nullptr, t, E, K, part, logit);
+    if (warp != 0) return;
+    float z[ROUTE_MAX_PER_LANE], c[ROUTE_MAX_PER_LANE];
+    float m = -INFINITY;
+#pragma unroll
+    for (int k = 0; k < ROUTE_MAX_PER_LANE; ++k) {
+        const int e = lane + 32 * k;
+        z[k] = e < E ? logit[e] : -INFINITY;
+        m = fmaxf(m, z[k]);
+    }
+    m = warp_max(m);
+    float sum = 0.0f;
+#pragma unroll
+    for (int k = 0; k < ROUTE_MAX_PER_LANE; ++k) {
+        z[k] = lane + 32 * k < E ? expf(z[k] - m) : 0.0f;
+        sum += z[k];
+    }
+    sum = warp_sum(sum);
+#pragma unroll
+    for (int k = 0; k < ROUTE_MAX_PER_LANE; ++k) {
+        const int e = lane + 32 * k;
+        z[k] = z[k] / sum;                            // the score s
+        c[k] = e < E ? z[k] + (correction != nullptr ? correction[e] : 0.0f) : -INFINITY;
+        if (e < E) {
+            prob[e] = z[k];
+            logit[e] = c[k];                          // the choice scores, for the groups
+        }
+    }
+    __syncwarp();
+    if (G > 1 && keep < G) {
+        const int gs = E / G;
+        for (int g = lane; g < G; g += 32) {
+            float best = -INFINITY;
+            for (int j = 0; j < gs; ++j) best = fmaxf(best, logit[g * gs + j]);
+            gscore[g] = best;
+        }
+        __syncwarp();
+        // the `keep` best groups, one a round (the lower index wins a tie); a kept group's score is replaced by +infinity
+        for (int r = 0; r < keep; ++r) {
+            float best = -INFINITY;
+            int where = 0x7fffffff;
+            for (int g = lane; g < G; g += 32) {
+                const float v = gscore[g];
+                if (v != INFINITY && (where == 0x7fffffff || v > best)) {
+                    best = v;
+                    where = g;
+                }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                const int ow = __shfl_xor_sync(0xffffffffu, where, o);
+                if (ow != 0x7fffffff && (where == 0x7fffffff || ob > best || (ob == best && ow < where))) {
+                    best = ob;
+                    where = ow;
+                }
+            }
+            if (lane == 0 && where != 0x7fffffff) gscore[where] = INFINITY;      // kept
+            __syncwarp();
+        }
+#pragma unroll
+        for (int k = 0; k < ROUTE_MAX_PER_LANE; ++k) {
+            const int e = lane + 32 * k;
+            if (e < E && gscore[e / gs] != INFINITY) c[k] = -INFINITY;
+        }
+    }
+    float mine = 0.0f;                                // lane j keeps the score s of the j-th chosen expert
+    for (int j = 0; j < top; ++j) {
+        float best = -INFINITY;
+        int where = 0x7fffffff;
+#pragma unroll
+        for (int k = 0; k < ROUTE_MAX_PER_LANE; ++k) {
+            const int e = lane + 32 * k;
+            if (e < E && c[k] != -INFINITY && (where == 0x7fffffff || c[k] > best || (c[k] == best && e < where))) {
+                best = c[k];
+                where = e;
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int ow = __shfl_xor_sync(0xffffffffu, where, o);
+            if (ow != 0x7fffffff && (where == 0x7fffffff || ob > best || (ob == best && ow < where))) {
+                best = ob;
+                where = ow;
+            }
+        }
+        if (where != 0x7fffffff && (where & 31) == lane) {
+#pragma unroll
+            for (int k = 0; k < ROUTE_MAX_PER_LANE; ++k)
+                if (k == (where >> 5)) c[k] = -INFINITY;
+        }
+        if (where == 0x7fffffff) where = 0;
+        if (lane == j) mine = prob[where];
+        if (lane == 0) ids[(long long)t * top + j] = where;
+    }
+    const float total = warp_sum(lane < top ? mine : 0.0f);
+    if (lane < top) weights[(long long)t * top + lane] = mine / (total + 1e-20f) * scale;
+}
+
 // One block of 32 warps.  Warp w takes the w-th stretch of the pairs.  Shared: cnt[w][e], the pairs of expert e in
 // stretch w, turned into the row at which stretch w's pairs of expert e begin; inside a stretch the pairs of an expert
 // keep their order (lanes that hold the same expert find each other with match.any), so an expert's rows are its pairs in
@@ -117,9 +245,11 @@ moe_plan_kernel(const int* __restrict__ ids, int n_pairs, int top, int E, int ti
     for (int r = threadIdx.x; r < max_rows; r += blockDim.x) src_tok[r] = -1;
     for (int t = threadIdx.x; t < max_rows / tile; t += blockDim.x) tile_expert[t] = -1;
     __syncthreads();
+    // a pair whose id is E or more belongs to an expert without matrices (an identity expert): it takes no row, and its
+    // row_of is -1
     for (int p0 = p_begin; p0 < p_end; p0 += 32) {
         const int p = p0 + lane;
-        const bool have = p < p_end;
+        const bool have = p < p_end && ids[p] < E;
         const int e = have ? ids[p] : -1 - lane;                     // lanes without a pair match nobody
         const unsigned same = __match_any_sync(0xffffffffu, e);
         if (have && (same & ((1u << lane) - 1u)) == 0) cnt[warp * E + e] += __popc(same);      // the first lane of each expert
@@ -144,7 +274,8 @@ moe_plan_kernel(const int* __restrict__ ids, int n_pairs, int top, int E, int ti
     __syncthreads();
     for (int p0 = p_begin; p0 < p_end; p0 += 32) {
         const int p = p0 + lane;
-        const bool have = p < p_end;
+        const bool have = p < p_end && ids[p] < E;
+        if (p < p_end && !have) row_of[p] = -1;
         const int e = have ? ids[p] : -1 - lane;
         const unsigned same = __match_any_sync(0xffffffffu, e);
         if (have) {
@@ -226,13 +357,18 @@ __global__ void moe_gather_kernel(const T* __restrict__ x, const int* __restrict
     for (int i = threadIdx.x; i < d; i += blockDim.x) rows[(long long)r * d + i] = s >= 0 ? x[(long long)s * d + i] : from_float<T>(0.0f);
 }
 
+// A negative row stands for the token's own input, `ident` [n][d] (TI), if given; else it adds nothing.
+template <typename TI>
 __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ row_of, const float* __restrict__ weights,
-                                   int top, int d, float* __restrict__ out) {
+                                   const TI* __restrict__ ident, int top, int d, float* __restrict__ out) {
     const int t = blockIdx.x;
     for (int i = threadIdx.x; i < d; i += blockDim.x) {
         float acc = 0.0f;
-        for (int j = 0; j < top; ++j)
-            acc = fmaf(weights[(long long)t * top + j], y[(long long)row_of[(long long)t * top + j] * d + i], acc);
+        for (int j = 0; j < top; ++j) {
+            const int r = row_of[(long long)t * top + j];
+            const float e = r >= 0 ? y[(long long)r * d + i] : (ident != nullptr ? to_float(ident[(long long)t * d + i]) : 0.0f);
+            acc = fmaf(weights[(long long)t * top + j], e, acc);
+        }
         out[(long long)t * d + i] = acc;
     }
 }
@@ -323,6 +459,24 @@ extern "C" int mlc_moe_route(const void* x, int x_dtype, const float* w, const f
     return 0;
 }
 
+// x: the branch's input [n][K] of x_dtype; w float32 [E][K]; correction float32 [E] or null.  G groups of which `keep` stay
+// (G <= 1 or keep >= G: no grouping; E must be a multiple of G).
+extern "C" int mlc_moe_route_scored(const void* x, int x_dtype, const float* w, const float* correction, int n, int E, int K,
+                                    int top, int G, int keep, float scale, int* ids, float* weights, void* stream) {
+    if (n <= 0) return 0;
+    if (E <= 0 || E > 32 * ROUTE_MAX_PER_LANE || top <= 0 || top > 32 || top > E || K <= 0 || w == nullptr) return MLC_ERR_BAD_SIZE;
+    if (G > 1 && (E % G != 0 || keep < 1)) return MLC_ERR_BAD_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (x_dtype == MLC_DTYPE_F32)
+        moe_route_scored_kernel<float><<<n, 128, 0, s>>>((const float*)x, w, correction, n, E, K, top, G, keep, scale, ids, weights);
+    else if (x_dtype == MLC_DTYPE_BF16)
+        moe_route_scored_kernel<bf16><<<n, 128, 0, s>>>((const bf16*)x, w, correction, n, E, K, top, G, keep, scale, ids, weights);
+    else
+        return MLC_ERR_BAD_DTYPE;
+    MLC_LAUNCH_CHECK();
+    return 0;
+}
+
 extern "C" int mlc_moe_plan(const int* ids, int n_pairs, int top, int E, int tile, int max_rows, int* row_of, int* src_tok,
                             int* tile_expert, void* stream) {
     if (n_pairs <= 0) return 0;
@@ -378,11 +532,14 @@ extern "C" int mlc_moe_gather(const void* x, int dtype, const int* src_tok, int 
     return 0;
 }
 
-extern "C" int mlc_moe_combine(const float* y, const int* row_of, const float* weights, int n, int top, int d, float* out,
-                               void* stream) {
+extern "C" int mlc_moe_combine(const float* y, const int* row_of, const float* weights, const void* ident, int ident_dtype, int n,
+                               int top, int d, float* out, void* stream) {
     if (n <= 0) return 0;
     if (top <= 0 || d <= 0) return MLC_ERR_BAD_SIZE;
-    moe_combine_kernel<<<n, d >= 256 ? 256 : 64, 0, (cudaStream_t)stream>>>(y, row_of, weights, top, d, out);
+    if (ident != nullptr && ident_dtype == MLC_DTYPE_BF16)
+        moe_combine_kernel<bf16><<<n, d >= 256 ? 256 : 64, 0, (cudaStream_t)stream>>>(y, row_of, weights, (const bf16*)ident, top, d, out);
+    else
+        moe_combine_kernel<float><<<n, d >= 256 ? 256 : 64, 0, (cudaStream_t)stream>>>(y, row_of, weights, (const float*)ident, top, d, out);
     MLC_LAUNCH_CHECK();
     return 0;
 }

@@ -717,7 +717,8 @@ __global__ void gated_rmsnorm_kernel(const float* __restrict__ o, int n_slices, 
         for (int sl = 1; sl < n_slices; ++sl) v += src0[sl * slice_stride + d];
         return v;
     };
-    const float* g = gate + token * gate_stride + (long long)head * vdim;
+    const bool gated = gate != nullptr;               // no gate: the head norm alone
+    const float* g = gated ? gate + token * gate_stride + (long long)head * vdim : src0;
     if (vdim <= 256) {                              // the row, its gates and gains in registers: every load issued at once
         float v[8], z[8], wv[8];
 #pragma unroll
@@ -735,7 +736,7 @@ __global__ void gated_rmsnorm_kernel(const float* __restrict__ o, int n_slices, 
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
             const int d = lane + 32 * k;
-            if (d < vdim) out[row * vdim + d] = from_float<T>(v[k] * f * wv[k] * (z[k] * sigmoid_f(z[k])));
+            if (d < vdim) out[row * vdim + d] = from_float<T>(v[k] * f * wv[k] * (gated ? z[k] * sigmoid_f(z[k]) : 1.0f));
         }
         return;
     }
@@ -748,7 +749,7 @@ __global__ void gated_rmsnorm_kernel(const float* __restrict__ o, int n_slices, 
     const float f = 1.0f / sqrtf(ss / (float)vdim + eps);
     for (int d = lane; d < vdim; d += 32) {
         const float z = g[d];
-        out[row * vdim + d] = from_float<T>(src_at(d) * f * w[d] * (z * sigmoid_f(z)));
+        out[row * vdim + d] = from_float<T>(src_at(d) * f * w[d] * (gated ? z * sigmoid_f(z) : 1.0f));
     }
 }
 

@@ -19,6 +19,7 @@ __all__ = [
     "linear_scan", "gates_scan_step", "gates_scan_step_takes",
     "moe_route", "moe_plan", "moe_plan_rows", "grouped_linear", "moe_gather", "moe_combine", "scaled_add", "scaled_add_experts", "gla", "gla_slices", "latent_prepare",
     "head_project", "gemm_tcgen05_grouped", "GROUPED_TILE",
+    "group_norm", "activation", "forget_gate_attention", "moe_route_scored",
 ]
 
 
@@ -89,7 +90,7 @@ def core() -> ctypes.CDLL:
         lib = _build.core_library()
         P, I, F, LL = c_void_p, c_int, c_float, c_longlong
         sigs = {
-            "mlc_embed": [P, I, P, I, I, P, P],
+            "mlc_embed": [P, I, P, I, I, F, P, P],
             "mlc_add_rmsnorm": [P, P, I, P, F, I, I, P, I, P],
             "mlc_rope_table": [P, I, I, F, P, P],
             "mlc_layernorm": [P, P, I, P, F, I, I, I, P, I, P],
@@ -110,11 +111,15 @@ def core() -> ctypes.CDLL:
             "mlc_moe_plan": [P, I, I, I, I, I, P, P, P, P],
             "mlc_grouped_linear": [P, I, P, P, I, P, I, I, I, I, P, I, P],
             "mlc_moe_gather": [P, I, P, I, I, P, P],
-            "mlc_moe_combine": [P, P, P, I, I, I, P, P],
+            "mlc_moe_combine": [P, P, P, P, I, I, I, I, P, P],
+            "mlc_moe_route_scored": [P, I, P, P, I, I, I, I, I, I, F, P, P, P],
+            "mlc_group_norm": [P, LL, I, I, I, P, I, F, F, P, I, P, P, P, I, P, I, P, LL, P, I, P, I, P],
+            "mlc_activation": [P, I, LL, I, P, I, P],
+            "mlc_forget_gate_attention": [P, LL, I, I, I, P, P, P, P, P, LL, P, P, I, I, I, I, I, I, P, P],
             "mlc_scaled_add": [P, P, I, P, P, I, P, LL, I, P],
             "mlc_scaled_add_experts": [P, P, I, P, P, P, P, I, P, LL, I, P],
             "mlc_gla": [P, LL, I, I, I, P, P, F, P, LL, P, P, I, I, I, I, I, I, P, P],
-            "mlc_latent_prepare": [P, LL, I, I, P, F, P, P, P, I, I, I, I, I, I, I, P, I, I, P, P, LL, I, I, P],
+            "mlc_latent_prepare": [P, LL, P, LL, I, I, I, P, F, P, P, P, I, I, I, I, I, I, I, P, I, I, P, P, LL, I, I, P],
             "mlc_head_project": [P, I, LL, LL, P, I, LL, LL, LL, P, I, LL, LL, I, I, I, I, P],
             "mlc_linear_simt": [P, I, P, I, P, I, I, I, I, P, LL, I, P],
             "mlc_attention_combine": [P, P, LL, I, I, P, I, P, I, P],
@@ -187,11 +192,12 @@ class KVView:
         return self.page_table.shape[1]
 
 
-def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
+def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, scale: float = 1.0) -> None:
+    """out[t] = table[ids[t]] · scale, float32."""
     require_cuda(table, ids, out)
     n, d = out.shape
     assert ids.dtype == torch.int32 and ids.numel() == n and table.shape[1] == d and out.dtype == torch.float32
-    _check(core().mlc_embed(table.data_ptr(), dtype_code(table.dtype), ids.data_ptr(), n, d, out.data_ptr(), _stream()),
+    _check(core().mlc_embed(table.data_ptr(), dtype_code(table.dtype), ids.data_ptr(), n, d, float(scale), out.data_ptr(), _stream()),
            "embedding")
 
 
@@ -474,15 +480,16 @@ def gated_delta_rule(qkv: torch.Tensor, q_col: int, k_col: int, v_col: int, gate
     count_launches(1)
 
 
-def gated_rmsnorm(o: torch.Tensor, gate: torch.Tensor, gate_col: int, gain: torch.Tensor, eps: float, heads: int,
+def gated_rmsnorm(o: torch.Tensor, gate: Optional[torch.Tensor], gate_col: int, gain: torch.Tensor, eps: float, heads: int,
                   vdim: int, out: torch.Tensor) -> None:
     """out[t, h, :] = o[t, h, :] / rms · gain · silu(gate[t, gate_col + h*vdim + :]) per head (o float32 [n, heads*vdim], or
-    partial sums [slices, n, heads*vdim] that are added up first)."""
+    partial sums [slices, n, heads*vdim] that are added up first).  Without `gate` the head norm alone."""
     require_cuda(o, gain, out)
     n = o.shape[-2]
     slices = o.shape[0] if o.dim() == 3 else 1
     assert o.dtype == torch.float32 and gain.dtype == torch.float32 and gain.numel() == vdim and tuple(out.shape) == tuple(o.shape[-2:])
-    _check(core().mlc_gated_rmsnorm(o.data_ptr(), slices, _columns(gate, gate_col), gate.stride(0), gain.data_ptr(), float(eps), n,
+    _check(core().mlc_gated_rmsnorm(o.data_ptr(), slices, _columns(gate, gate_col) if gate is not None else None,
+                                    gate.stride(0) if gate is not None else 0, gain.data_ptr(), float(eps), n,
                                     heads, vdim, out.data_ptr(), dtype_code(out.dtype), _stream()), "gated head norm")
 
 
@@ -600,13 +607,34 @@ def moe_gather(x: torch.Tensor, src_tok: torch.Tensor, rows: torch.Tensor) -> No
                                  rows.data_ptr(), _stream()), "expert gather")
 
 
-def moe_combine(y: torch.Tensor, row_of: torch.Tensor, weights: torch.Tensor, out: torch.Tensor) -> None:
-    """out[t] = sum_j weights[t, j] · y[row_of[t, j]], float32, j in order."""
-    require_cuda(y, row_of, weights, out)
+def moe_combine(y: torch.Tensor, row_of: torch.Tensor, weights: torch.Tensor, out: torch.Tensor,
+                ident: Optional[torch.Tensor] = None) -> None:
+    """out[t] = sum_j weights[t, j] · y[row_of[t, j]], float32, j in order.  A negative row stands for the token's own row of
+    `ident` [n, d] (an identity expert); without `ident` it adds nothing."""
+    require_cuda(y, row_of, weights, out, ident)
     n, top = row_of.shape
     assert y.dtype == out.dtype == weights.dtype == torch.float32 and out.shape == (n, y.shape[1])
-    _check(core().mlc_moe_combine(y.data_ptr(), row_of.data_ptr(), weights.data_ptr(), n, top, y.shape[1], out.data_ptr(),
+    assert ident is None or tuple(ident.shape) == tuple(out.shape)
+    _check(core().mlc_moe_combine(y.data_ptr(), row_of.data_ptr(), weights.data_ptr(), _ptr(ident),
+                                  dtype_code(ident.dtype) if ident is not None else 0, n, top, y.shape[1], out.data_ptr(),
                                   _stream()), "expert combine")
+
+
+def moe_route_scored(x: torch.Tensor, router: torch.Tensor, correction: Optional[torch.Tensor], top: int, groups: int, keep: int,
+                     scale: float, ids: torch.Tensor, weights: torch.Tensor) -> None:
+    """Routing by the softmax s over all router outputs (router float32 [E, K], x the branch's input [n, K]; logits in
+    float32): chosen are the `top` largest s + correction among the experts of the `keep` best of `groups` equal groups of
+    neighbours (a group's score: its largest choice score; groups <= 1: no grouping); weights = s of the chosen, divided
+    by their sum + 1e-20, times `scale`.  ids int32 [n, top], weights float32 [n, top]."""
+    require_cuda(x, router, correction, ids, weights)
+    n = x.shape[0]
+    E, K = router.shape
+    assert router.dtype == torch.float32 and x.shape[1] == K
+    assert ids.dtype == torch.int32 and weights.dtype == torch.float32 and ids.shape == (n, top) and weights.shape == (n, top)
+    assert correction is None or (correction.dtype == torch.float32 and correction.numel() == E)
+    _check(core().mlc_moe_route_scored(x.data_ptr(), dtype_code(x.dtype), router.data_ptr(), _ptr(correction), n, E, K, int(top),
+                                       int(groups), int(keep), float(scale), ids.data_ptr(), weights.data_ptr(), _stream()),
+           "expert routing by scores")
 
 
 def scaled_add(x: torch.Tensor, y1: torch.Tensor, s1: Optional[torch.Tensor], y2: Optional[torch.Tensor] = None,
@@ -667,14 +695,96 @@ def gla(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, z: torch.Tensor,
     count_launches(1)
 
 
+def forget_gate_attention(proj: torch.Tensor, q_col: int, f_col: int, v_col: int, f_bias: Optional[torch.Tensor],
+                          lower: Optional[torch.Tensor], state: torch.Tensor, step, heads: int, dim: int, vdim: int,
+                          out: torch.Tensor) -> None:
+    """The forget-gate form of gated linear attention over the step's tokens: f = l + (1 - l) sigmoid(z_f + b),
+    S <- diag(f) S + (1 - f) vT, o = ST silu(z_q); z_q, z_f (heads x dim) and v (heads x vdim) in the float32 rows `proj`,
+    f_bias and lower float32 [heads*dim] or None, state float32 [slots, heads*vdim*dim], out float32
+    [gla_slices(...), n, heads*vdim]: partial outputs whose sum over the first axis is o."""
+    require_cuda(f_bias, lower, out)
+    _require_rows(state)
+    n = proj.shape[0]
+    lib = core()
+    rows = lib.mlc_gla_rows(step.n_seqs, heads, dim, vdim, _sm_count(out.device))
+    slices = (dim + 8 * rows - 1) // (8 * rows)
+    assert proj.dtype == out.dtype == torch.float32 and tuple(out.shape) == (slices, n, heads * vdim)
+    assert state.shape[1] == heads * dim * vdim
+    for t in (f_bias, lower):
+        assert t is None or (t.dtype == torch.float32 and t.numel() == heads * dim)
+    qk = torch.empty((n, 2 * heads * dim), dtype=torch.float32, device=out.device)
+    decay = torch.empty((n, heads * dim), dtype=torch.float32, device=out.device)
+    _check(lib.mlc_forget_gate_attention(_columns(proj, 0), proj.stride(0), q_col, f_col, v_col, _ptr(f_bias), _ptr(lower),
+                                         qk.data_ptr(), decay.data_ptr(), state.data_ptr(), state.stride(0),
+                                         step.slots.data_ptr(), step.cu_seqlens.data_ptr(), step.n_seqs, n, heads, dim, vdim, rows,
+                                         out.data_ptr(), _stream()), "forget-gate linear attention")
+    count_launches(1)
+
+
+# ------------------------------------------------------------------ norm in groups, activations (csrc/group_norm.cu)
+def group_norm(x: torch.Tensor, groups: int, gain: torch.Tensor, eps: float, out: Optional[torch.Tensor] = None,
+               write_x: bool = False, alpha: float = 1.0, y: Optional[torch.Tensor] = None, expert_rows=None,
+               gate: Optional[torch.Tensor] = None, gate_col: int = 0, gate_bias: Optional[torch.Tensor] = None) -> None:
+    """RMS norm in `groups` equal consecutive parts of each row of x (float32 [n, d], rows may be strided), each part by its
+    own root mean square (eps inside the root), times `gain` (float32, as long as the row or as one part).  With a
+    branch, the norm is of alpha · x + s * b first: b = `y` (float32 [n, d] or slices [s, n, d] added up) or the weighted
+    sum of `expert_rows` = (rows float32 [., d], row_of int32 [n, top], weights float32 [n, top], ident [n, d] or None: the
+    row a negative row_of stands for); s = sigmoid(gate[:, gate_col:gate_col + d] + gate_bias) when `gate` (float32 rows)
+    is given, else one.  The result goes into x itself (`write_x`) and/or `out` [n, d] in its own type."""
+    require_cuda(gain, out, y, gate_bias)
+    n, d = x.shape
+    assert x.dtype == torch.float32 and x.stride(1) == 1 and gain.dtype == torch.float32
+    assert out is not None or write_x
+    assert out is None or tuple(out.shape) == (n, d)
+    slices = 0
+    if y is not None:
+        assert y.dtype == torch.float32 and tuple(y.shape[-2:]) == (n, d)
+        slices = y.shape[0] if y.dim() == 3 else 1
+    rows = row_of = weights = ident = None
+    top = 0
+    if expert_rows is not None:
+        rows, row_of, weights, ident = expert_rows
+        require_cuda(rows, row_of, weights, ident)
+        top = row_of.shape[1]
+        assert y is None and rows.dtype == weights.dtype == torch.float32 and row_of.dtype == torch.int32 and rows.shape[1] == d
+        assert row_of.shape == weights.shape and row_of.shape[0] == n and (ident is None or tuple(ident.shape) == (n, d))
+    if gate is not None:
+        assert gate.dtype == torch.float32 and gate.stride(1) == 1 and gate.shape[0] == n and gate_col + d <= gate.shape[1]
+        assert gate_bias is None or (gate_bias.dtype == torch.float32 and gate_bias.numel() == d)
+    _check(core().mlc_group_norm(x.data_ptr(), x.stride(0), n, d, int(groups), gain.data_ptr(), gain.numel(), float(eps),
+                                 float(alpha), _ptr(y), slices, _ptr(rows), _ptr(row_of), _ptr(weights), top, _ptr(ident),
+                                 dtype_code(ident.dtype) if ident is not None else 0,
+                                 _columns(gate, gate_col) if gate is not None else None, gate.stride(0) if gate is not None else 0,
+                                 _ptr(gate_bias) if gate is not None else None, 1 if write_x else 0, _ptr(out),
+                                 dtype_code(out.dtype) if out is not None else 0, _stream()), "norm in groups")
+
+
+ACTIVATIONS = {"silu": 0, "gelu": 1, "gelu_tanh": 2}
+
+
+def activation(src: torch.Tensor, kind: str, out: torch.Tensor) -> None:
+    """out = act(src) elementwise in float32 arithmetic: "silu", "gelu" (with erf) or "gelu_tanh"."""
+    require_cuda(src, out)
+    assert src.numel() == out.numel()
+    if kind not in ACTIVATIONS:
+        raise KernelError(f"activation {kind!r} is not one of {', '.join(ACTIVATIONS)}")
+    _check(core().mlc_activation(src.data_ptr(), dtype_code(src.dtype), src.numel(), ACTIVATIONS[kind], out.data_ptr(),
+                                 dtype_code(out.dtype), _stream()), "activation")
+
+
 # ------------------------------------------------------------------ latent attention (csrc/latent.cu)
 def latent_prepare(proj: torch.Tensor, q_col: int, kv_col: int, gain: torch.Tensor, eps: float, positions: torch.Tensor,
                    tok_seq: torch.Tensor, rope: Optional[torch.Tensor], heads: int, dim: int, rot: int, rank: int,
-                   q_out: torch.Tensor, kv: Optional[KVView]) -> None:
+                   q_out: torch.Tensor, kv: Optional[KVView], q_rows: Optional[torch.Tensor] = None,
+                   interleaved: bool = False) -> None:
     """From the float32 rows `proj` (query heads [dim | rot] at q_col, [rank | rot] at kv_col): the cache row
     [normed latent | rotated shared key part | zeros] of every token (when `kv` is given), and the rotated query parts
-    into entries [rank, rank + rot) of q_out [n, heads, D] (zeros behind them)."""
+    into entries [rank, rank + rot) of q_out [n, heads, D] (zeros behind them).  With `q_rows` (float32 rows) the query
+    heads are read from there instead, at q_col.  `interleaved`: the rotation pairs entry 2i with 2i + 1, not i with
+    i + rot/2."""
     require_cuda(proj, gain, positions, tok_seq, rope, q_out)
+    qsrc = proj if q_rows is None else q_rows
+    assert qsrc.dtype == torch.float32 and qsrc.dim() == 2 and qsrc.stride(1) == 1 and qsrc.shape[0] == proj.shape[0]
     n = proj.shape[0]
     D = q_out.numel() // max(1, n * heads)
     assert proj.dtype == torch.float32 and gain.dtype == torch.float32 and gain.numel() == rank
@@ -684,7 +794,8 @@ def latent_prepare(proj: torch.Tensor, q_col: int, kv_col: int, gain: torch.Tens
         args = (1, kv.k_pool.data_ptr(), kv.page_table.data_ptr(), kv.entry_offset, kv.pages_per_seq, kv.page_size)
     else:
         args = (0, None, None, 0, 0, 1)
-    _check(core().mlc_latent_prepare(proj.data_ptr(), proj.stride(0), q_col, kv_col, gain.data_ptr(), float(eps),
+    _check(core().mlc_latent_prepare(proj.data_ptr(), proj.stride(0), qsrc.data_ptr(), qsrc.stride(0), 1 if interleaved else 0,
+                                     q_col, kv_col, gain.data_ptr(), float(eps),
                                      positions.data_ptr(), tok_seq.data_ptr(), _ptr(rope), rope.shape[0] if rope is not None else 0,
                                      n, heads, dim, rot, rank, D, q_out.data_ptr(), dtype_code(q_out.dtype), *args, _stream()),
            "latent norm, rotation and cache write")
@@ -880,6 +991,8 @@ def attention_mma(q: torch.Tensor, out: torch.Tensor, cu_seqlens: torch.Tensor, 
 
 
 EPI_STORE, EPI_SILU_MUL, EPI_QKV, EPI_ADD = 0, 1, 2, 3
+# the grouped product only: EPI_STORE behind an activation of the product, in float32
+EPI_ACT = {"silu": 4, "gelu": 5, "gelu_tanh": 6}
 _status = {}
 
 
@@ -1125,7 +1238,7 @@ def gemm_tcgen05_grouped(x: torch.Tensor, w: torch.Tensor, tile_group: torch.Ten
     """The prompt form of the tcgen05 product with a matrix per group of rows (csrc/gemm_tcgen05_rows.cu): bfloat16 x
     [rows, K], rows a multiple of 128; bfloat16 w [groups, n_out, K]; tile_group int32 [rows / 128] gives every tile of
     128 rows its group (negative: skipped).  EPI_STORE: out [rows, n_out]; EPI_SILU_MUL (w's rows alternate gate and
-    up): out [rows, n_out / 2]."""
+    up): out [rows, n_out / 2]; EPI_ACT[name]: out [rows, n_out] = act(product)."""
     require_cuda(x, w, tile_group, out)
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise KernelError("the tcgen05 matrix product takes bfloat16 operands")

@@ -260,6 +260,8 @@ class SinkAttention(GQAttention):
         self.value_scale = float(value_scale)
         self.t = {role: name + n for role, n in {**self.NAMES, **(names or {})}.items()}
         self.position = build_part(position, name)
+        if getattr(self.position, "interleaved", False):
+            raise ValueError("attention: this mixer's kernel rotates the pairs (i, i + dims/2) only")
         self.sinks: Optional[torch.Tensor] = None
 
     def tensors(self):
@@ -346,18 +348,28 @@ class LatentAttention(GQAttention):
     to the head's weighted sum of latents, so a step never expands the keys and values of the tokens before it.  The
     attention kernels are the ones every other attention uses.
 
-    `names`: the tensors' names below the part's prefix, by role (q, dkv, dkv_norm, uk, uv, o)."""
+    Options.  `q_rank`: the queries go through a latent of their own, c_q = rms(W_dq h) · g_q (eps inside the root),
+    q = W_uq c_q (tensors dq, dq_norm, uq instead of q).  `window`: position i sees the keys j with 0 <= i - j < window
+    (no window: every j <= i); the cache then keeps a window of rows.  The position part's `interleaved` says which
+    entries of the rotated part form a pair.
+
+    Offers `in_weights()`, `in_width()`, `mix()` and `o` to an arrangement that computes other matrices on the same input
+    in the mixer's input product.
+
+    `names`: the tensors' names below the part's prefix, by role (q, dq, dq_norm, uq, dkv, dkv_norm, uk, uv, o)."""
     graph_safe = True
     accumulates = False
 
-    NAMES = dict(q="q", dkv="dkv", dkv_norm="dkv.norm", uk="uk", uv="uv", o="o")
+    NAMES = dict(q="q", dq="dq", dq_norm="dq.norm", uq="uq", dkv="dkv", dkv_norm="dkv.norm", uk="uk", uv="uv", o="o")
 
     def __init__(self, name: str, hidden_size: int, num_heads: int, head_dim: int, rot_dim: int, v_head_dim: int, kv_rank: int,
-                 scale: float, norm_eps: float, position: PartSpec, names: Optional[dict] = None):
+                 scale: float, norm_eps: float, position: PartSpec, names: Optional[dict] = None, q_rank: Optional[int] = None,
+                 window: Optional[int] = None):
         Part.__init__(self, name, hidden_size=hidden_size, num_heads=num_heads, head_dim=head_dim, rot_dim=rot_dim,
-                      v_head_dim=v_head_dim, kv_rank=kv_rank, scale=scale, norm_eps=norm_eps)
+                      v_head_dim=v_head_dim, kv_rank=kv_rank, scale=scale, norm_eps=norm_eps, q_rank=q_rank, window=window)
         self.hidden, self.H, self.KV = int(hidden_size), int(num_heads), 1
         self.dim, self.rot, self.vdim, self.rank = int(head_dim), int(rot_dim), int(v_head_dim), int(kv_rank)
+        self.q_rank = int(q_rank) if q_rank else None
         if self.rot % 2 or self.rot < 0 or self.dim < 0 or self.dim + self.rot <= 0:
             raise ValueError(f"latent attention: a head has {head_dim} plain and {rot_dim} rotated entries; the rotated size must be even")
         self.hd = (self.rank + self.rot + 15) // 16 * 16              # a cached row, and a query row, in the kernels
@@ -366,26 +378,39 @@ class LatentAttention(GQAttention):
         if not scale > 0:
             raise ValueError(f"latent attention: the score's scale must be positive, got {scale}")
         self.scale, self.eps = float(scale), float(norm_eps)
-        self.window = None
+        self.window = int(window) if window else None
         self.t = {role: name + n for role, n in {**self.NAMES, **(names or {})}.items()}
         self.position = build_part(position, name)
+        self.interleaved = bool(getattr(self.position, "interleaved", False))
 
     def tensors(self):
         t, H = self.t, self.H
-        return [TensorSpec(t["q"], (H * (self.dim + self.rot), self.hidden)),
-                TensorSpec(t["dkv"], (self.rank + self.rot, self.hidden)),
-                TensorSpec(t["dkv_norm"], (self.rank,), role="gain", init="one_plus_normal"),
-                TensorSpec(t["uk"], (H * self.dim, self.rank)), TensorSpec(t["uv"], (H * self.vdim, self.rank)),
-                TensorSpec(t["o"], (self.hidden, H * self.vdim))]
+        nq = H * (self.dim + self.rot)
+        if self.q_rank:
+            q = [TensorSpec(t["dq"], (self.q_rank, self.hidden)),
+                 TensorSpec(t["dq_norm"], (self.q_rank,), role="gain", init="one_plus_normal"),
+                 TensorSpec(t["uq"], (nq, self.q_rank))]
+        else:
+            q = [TensorSpec(t["q"], (nq, self.hidden))]
+        return q + [TensorSpec(t["dkv"], (self.rank + self.rot, self.hidden)),
+                    TensorSpec(t["dkv_norm"], (self.rank,), role="gain", init="one_plus_normal"),
+                    TensorSpec(t["uk"], (H * self.dim, self.rank)), TensorSpec(t["uv"], (H * self.vdim, self.rank)),
+                    TensorSpec(t["o"], (self.hidden, H * self.vdim))]
 
     def cache_need(self) -> CacheNeed:
-        return CacheNeed("all", 1, self.hd, None, 0, True)
+        return CacheNeed("window" if self.window else "all", 1, self.hd, self.window, 0, True)
 
     def bind(self, get, runtime):
         Part.bind(self, get, runtime)
         t = self.t
-        self.in_proj = fused_rows([get(t["q"]), get(t["dkv"])], runtime)
-        self.kv_col = self.H * (self.dim + self.rot)
+        # columns of the input product: [q heads | latent | shared rotated key part], or with a query latent
+        # [query latent | latent | shared rotated key part]
+        self._in = [get(t["dq"]) if self.q_rank else get(t["q"]), get(t["dkv"])]
+        self.in_proj: Optional[Linear] = None
+        self.kv_col = self._in[0].shape[0]
+        if self.q_rank:
+            self.q_gain = get(t["dq_norm"]).to(torch.float32).contiguous()
+            self.uq = Linear(get(t["uq"]), runtime)
         self.gain = get(t["dkv_norm"]).to(torch.float32).contiguous()
         self.w_uk, self.w_uv = get(t["uk"]).contiguous(), get(t["uv"]).contiguous()
         self.o = Linear(get(t["o"]), runtime)
@@ -395,26 +420,43 @@ class LatentAttention(GQAttention):
         if self.use_tensor_cores:
             kernels.attention_library(self.hd)
 
+    def in_weights(self):
+        """The matrices that read the mixer's input, in the order of the columns `mix` expects."""
+        return list(self._in)
+
+    def in_width(self) -> int:
+        return self.kv_col + self.rank + self.rot
+
     def weight_bytes(self) -> int:
-        return (self.in_proj.nbytes() + self.o.nbytes()
-                + sum(w.numel() * w.element_size() for w in (self.w_uk, self.w_uv)))
+        b = sum(w.numel() * w.element_size() for w in self._in) + self.o.nbytes()
+        b += sum(w.numel() * w.element_size() for w in (self.w_uk, self.w_uv))
+        return b + (self.uq.nbytes() if self.q_rank else 0)
 
     def flops_per_token(self) -> float:
-        """Multiply-adds x 2 of the two per-head expansions."""
-        return 2.0 * self.H * self.rank * (self.dim + self.vdim)
+        """Multiply-adds x 2 of the two per-head expansions (and of the queries' expansion from their latent)."""
+        f = 2.0 * self.H * self.rank * (self.dim + self.vdim)
+        return f + (2.0 * self.q_rank * self.H * (self.dim + self.rot) if self.q_rank else 0.0)
 
-    def forward(self, h: torch.Tensor, step, memory: MixerMemory, residual: Optional[torch.Tensor] = None):
+    def mix(self, proj: torch.Tensor, col: int, step, memory: MixerMemory) -> torch.Tensor:
+        """Attention from the float32 projection rows `proj`, whose columns from `col` on are this mixer's input product;
+        returns the heads' values [n, heads·vdim] in the engine's type, the input of `self.o`."""
         rt = self.runtime
-        n, H, D = h.shape[0], self.H, self.hd
-        proj = self.in_proj(h, torch.float32)
+        n, H, D = proj.shape[0], self.H, self.hd
+        q_rows, q_col = None, col
+        if self.q_rank:
+            cq = rt.empty(n, self.q_rank)
+            kernels.group_norm(proj[:, col:col + self.q_rank], 1, self.q_gain, self.eps, out=cq)
+            q_rows, q_col = self.uq(cq, torch.float32), 0
+        qsrc = proj if q_rows is None else q_rows
         table = self.position.table_for(step.max_kv_len) if self.rot and hasattr(self.position, "table_for") else None
         q = rt.empty(n, H * D)
-        kernels.latent_prepare(proj, 0, self.kv_col, self.gain, self.eps, step.positions, step.tok_seq, table, H, self.dim,
-                               self.rot, self.rank, q, memory.kv if memory.writes_cache else None)
+        kernels.latent_prepare(proj, q_col, col + self.kv_col, self.gain, self.eps, step.positions, step.tok_seq, table, H,
+                               self.dim, self.rot, self.rank, q, memory.kv if memory.writes_cache else None, q_rows=q_rows,
+                               interleaved=self.interleaved)
         if self.dim:
             # the key expansion on the query's side: q'[t, h, :rank] = W_uk,hᵀ q_plain[t, h]
-            kernels.head_project(proj, (proj.stride(0), self.dim + self.rot), self.w_uk, (self.dim * self.rank, self.rank, 1),
-                                 q, (H * D, D), n, H, self.dim, self.rank)
+            kernels.head_project(qsrc, (qsrc.stride(0), self.dim + self.rot), self.w_uk, (self.dim * self.rank, self.rank, 1),
+                                 q, (H * D, D), n, H, self.dim, self.rank, src_offset=q_col)
         else:
             q.view(n, H, D)[:, :, :self.rank].zero_()
         o = rt.empty(n, H * D)
@@ -423,4 +465,10 @@ class LatentAttention(GQAttention):
         val = rt.empty(n, H * self.vdim)
         kernels.head_project(o, (H * D, D), self.w_uv, (self.vdim * self.rank, 1, self.rank), val, (H * self.vdim, self.vdim),
                              n, H, self.rank, self.vdim)
+        return val
+
+    def forward(self, h: torch.Tensor, step, memory: MixerMemory, residual: Optional[torch.Tensor] = None):
+        if self.in_proj is None:
+            self.in_proj = fused_rows(self._in, self.runtime)
+        val = self.mix(self.in_proj(h, torch.float32), 0, step, memory)
         return self.o(val, torch.float32, partial_ok=True)

@@ -41,7 +41,7 @@ class TensorSpec:
     shape: Tuple[int, ...]
     role: str = "matrix"
     optional: bool = False
-    init: str = "normal"        # "normal": N(0, std); "one_plus_normal": 1 + N(0, std)
+    init: str = "normal"        # "normal": N(0, std); "one_plus_normal": 1 + N(0, std); "unit_interval": uniform in (0.05, 0.95)
     stored: bool = True         # False: not a tensor of its own in the file (an alias of another part's)
     # A size of -1 in `shape` is one that only the file gives (no key of the configuration names it): any size fits, and
     # the part reads it off the tensor when it binds.  `default_shape` is what the random-weights mode writes then.

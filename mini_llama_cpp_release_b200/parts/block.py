@@ -103,6 +103,125 @@ class BranchNormBlock(Part):
         return x, None
 
 
+@register_part("block", "post_norm")
+class PostNormBlock(Part):
+    """Norm behind the sum: x <- N1(alpha · x + g1 * mixer(x)); x <- N2(alpha · x + g2 * feed_forward(x)).  The branches
+    read the stream itself (the stream is what the norm before left).  alpha weighs the stream against the branch.  With
+    `gated`, each branch's output is multiplied entry by entry by g = sigmoid(W_g x + b_g), a gate of the branch's own
+    computed from the branch's input (tensors `mixer_gate`, `mixer_gate_bias`, `feed_forward_gate`,
+    `feed_forward_gate_bias`); without, g = 1.  The feed-forward (with its norm and gate) may be absent.
+
+    The stream is float32 and so are the gate, the sum and the norm: one kernel (`kernels.group_norm`) forms
+    alpha · x + sigmoid(z + b) * branch, norms it, writes the stream back and, for an engine that computes in 16 bits, the
+    16-bit copy that the next branch reads (handed on in the step's `handover`, as the branch-norm block does).  The gate's
+    matrix rides in the mixer's input product when the mixer offers `in_weights / mix / o` (one product over
+    [W_g ; the mixer's own matrices]).  A mixture of experts that defers its weighted sum has it made by the same kernel."""
+    graph_safe = True
+
+    COPY = BranchNormBlock.COPY
+
+    def __init__(self, name: str, mixer: PartSpec, mixer_norm: PartSpec, feed_forward: Optional[PartSpec] = None,
+                 feed_forward_norm: Optional[PartSpec] = None, alpha: float = 1.0, gated: bool = False,
+                 names: Optional[dict] = None):
+        super().__init__(name, alpha=alpha, gated=gated)
+        names = names or {}
+        if (feed_forward is None) != (feed_forward_norm is None):
+            raise ValueError("post_norm block: a feed-forward and its norm come together or not at all")
+        self.alpha, self.gated = float(alpha), bool(gated)
+        self.mixer = build_part(mixer, name + names.get("mixer", "mixer."))
+        self.mixer_norm = build_part(mixer_norm, name + names.get("mixer_norm", "mixer_norm."))
+        self.feed_forward = build_part(feed_forward, name + names.get("feed_forward", "feed_forward.")) if feed_forward else None
+        self.feed_forward_norm = (build_part(feed_forward_norm, name + names.get("feed_forward_norm", "feed_forward_norm."))
+                                  if feed_forward_norm else None)
+        for norm in (self.mixer_norm, self.feed_forward_norm):
+            if norm is not None and not hasattr(norm, "renorm"):
+                raise ValueError("post_norm block: its norms must offer `renorm` (the norm of a gated residual sum)")
+        self.size = self.mixer_norm.size
+        self.t = {k: name + names.get(k, k) for k in ("mixer_gate", "mixer_gate_bias", "feed_forward_gate", "feed_forward_gate_bias")}
+
+    def children(self):
+        return tuple(p for p in (self.mixer, self.mixer_norm, self.feed_forward, self.feed_forward_norm) if p is not None)
+
+    def tensors(self):
+        if not self.gated:
+            return []
+        d, t = self.size, self.t
+        specs = [TensorSpec(t["mixer_gate"], (d, d)), TensorSpec(t["mixer_gate_bias"], (d,), role="bias")]
+        if self.feed_forward is not None:
+            specs += [TensorSpec(t["feed_forward_gate"], (d, d)), TensorSpec(t["feed_forward_gate_bias"], (d,), role="bias")]
+        return specs
+
+    def bind(self, get, runtime):
+        super().bind(get, runtime)
+        from .attention import fused_rows
+        from .linear import Linear
+        self.gate1 = self.gate2 = self.b1 = self.b2 = self.joint = None
+        self.side_by_side = all(hasattr(self.mixer, a) for a in ("in_weights", "mix", "o"))
+        if self.gated:
+            w1 = get(self.t["mixer_gate"])
+            self.b1 = get(self.t["mixer_gate_bias"]).to(torch.float32).contiguous()
+            if self.side_by_side:
+                self.joint = fused_rows([w1] + list(self.mixer.in_weights()), runtime)       # [gate | the mixer's columns]
+            else:
+                self.gate1 = Linear(w1, runtime)
+            if self.feed_forward is not None:
+                self.gate2 = Linear(get(self.t["feed_forward_gate"]), runtime)
+                self.b2 = get(self.t["feed_forward_gate_bias"]).to(torch.float32).contiguous()
+
+    def weight_bytes(self) -> int:
+        own = sum(l.nbytes() for l in (self.gate1, self.gate2) if l is not None)
+        if self.joint is not None:
+            own += self.size * self.size * self.joint.weight.element_size()
+        return super().weight_bytes() + own + sum(b.numel() * 4 for b in (self.b1, self.b2) if b is not None)
+
+    def _input(self, x: torch.Tensor, step) -> torch.Tensor:
+        """What a branch reads: the stream itself in a float32 engine, else its copy in the engine's type."""
+        rt = self.runtime
+        if rt.dtype == torch.float32:
+            return x
+        left = step.handover.pop(self.COPY, None)
+        if left is not None and left[0] is x:
+            return left[1]
+        h = rt.empty(*x.shape)
+        kernels.convert(x, h)
+        return h
+
+    def forward(self, x: torch.Tensor, pending: Optional[torch.Tensor], step, memory: MixerMemory
+                ) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+        rt = self.runtime
+        if pending is not None:                     # a block of another kind left a branch output to be added
+            x.add_(pending.sum(dim=0) if pending.dim() == 3 else pending)
+        copy_dtype = None if rt.dtype == torch.float32 else rt.dtype
+        h = self._input(x, step)
+        gate, gate_col = None, 0
+        if self.joint is not None:
+            proj = self.joint(h, torch.float32)
+            y = self.mixer.o(self.mixer.mix(proj, self.size, step, memory), torch.float32, partial_ok=True)
+            gate = proj
+        else:
+            if self.gate1 is not None:
+                gate = self.gate1(h, torch.float32)
+            y = self.mixer.forward(h, step, memory)
+        h = self.mixer_norm.renorm(x, self.alpha, y=y, gate=gate, gate_col=gate_col, gate_bias=self.b1, copy_dtype=copy_dtype)
+        if h is not None:
+            step.handover[self.COPY] = (x, h)
+        ff = self.feed_forward
+        if ff is not None:
+            h = self._input(x, step)
+            gate = self.gate2(h, torch.float32) if self.gate2 is not None else None
+            if getattr(ff, "defers_sum", False):
+                # a mixture of experts: the weighted sum of a token's expert rows is made by the kernel that norms
+                rows, row_of, weights = ff.forward(h, step, deferred=True)
+                h = self.feed_forward_norm.renorm(x, self.alpha, expert_rows=(rows, row_of, weights, h if getattr(ff, "identity", 0) else None),
+                                                  gate=gate, gate_bias=self.b2, copy_dtype=copy_dtype)
+            else:
+                h = self.feed_forward_norm.renorm(x, self.alpha, y=ff.forward(h, step), gate=gate, gate_bias=self.b2,
+                                                  copy_dtype=copy_dtype)
+            if h is not None:
+                step.handover[self.COPY] = (x, h)
+        return x, None
+
+
 @register_part("block", "parallel")
 class ParallelBlock(Part):
     """One norm, two branches that both read it: h = norm(x); x <- x + s1 * mixer(h) + s2 * feed_forward(h).

@@ -17,10 +17,10 @@ from .linear import Linear
 class TokenEmbedding(Part):
     graph_safe = True
 
-    def __init__(self, name: str, vocab_size: int, hidden_size: int, tensor: str = "weight"):
-        """`tensor`: the table's name below the part's prefix."""
-        super().__init__(name, vocab_size=vocab_size, hidden_size=hidden_size, tensor=tensor)
-        self.vocab, self.hidden = int(vocab_size), int(hidden_size)
+    def __init__(self, name: str, vocab_size: int, hidden_size: int, tensor: str = "weight", scale: float = 1.0):
+        """`tensor`: the table's name below the part's prefix.  `scale` multiplies every row as it is read (float32)."""
+        super().__init__(name, vocab_size=vocab_size, hidden_size=hidden_size, tensor=tensor, scale=scale)
+        self.vocab, self.hidden, self.scale = int(vocab_size), int(hidden_size), float(scale)
         self.tensor = self.name + tensor
 
     def tensors(self):
@@ -35,7 +35,7 @@ class TokenEmbedding(Part):
 
     def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
         x = self.runtime.empty(token_ids.numel(), self.hidden, dtype=torch.float32)
-        kernels.embed(self.table, token_ids, x)
+        kernels.embed(self.table, token_ids, x, self.scale)
         return x
 
 

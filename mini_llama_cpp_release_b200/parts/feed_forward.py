@@ -74,41 +74,76 @@ class SwiGLU(Part):
 
 @register_part("feed_forward", "mixture")
 class MixtureOfExperts(Part):
-    """A mixture of SwiGLU experts.  Router logits z = W_r h + b_r in float32; each token uses the `top` experts with the
-    largest logits, weighted by the softmax over those chosen logits only; the output is the weighted sum of the
-    chosen experts' outputs.  Experts have no biases.
+    """A mixture of experts.  The output is the weighted sum of the chosen experts' outputs; experts have no biases.
+
+    Experts: `gated=True`: SwiGLU, W_down (act(W_gate h) * W_up h); `gated=False`: W_down act(W_up h).  `activation`:
+    "silu", "gelu" (with erf) or "gelu_tanh" (the gated form takes silu only).
+
+    Routing, `routing="top_logits"`: router logits z = W_r h + b_r in float32; each token uses the `top` experts with the
+    largest logits, weighted by the softmax over those chosen logits only.  `routing="scores"`: s = softmax(z) over all
+    router outputs; chosen are the `top` largest s + correction (a stored per-expert term, `correction=True`) among the
+    experts of the `group_keep` best of `group_count` equal groups of neighbours (a group's score is its largest choice
+    score; one group: no grouping); the weights are s of the chosen (without the correction), divided by their sum
+    + 1e-20, times `weight_scale`.  `identity`: that many further router outputs, behind the experts', belong to identity
+    experts, which have no tensors and return their input; they take part in scores, groups and choice like the others.
 
     On the device and without a word to the host: the step's (token, expert) pairs are sorted by expert into runs that
     start on tile borders (`kernels.moe_plan`), every run's rows are multiplied by that expert's matrices, and each
     token adds up its rows with its weights, in the order of its choices.
 
-    `names`: the tensors' names below the part's prefix, by role: router, router_bias, and the pattern of an expert's
-    prefix (`expert`, with {e} for its number) before gate / up / down."""
+    `names`: the tensors' names below the part's prefix, by role: router, router_bias, correction, and the pattern of an
+    expert's prefix (`expert`, with {e} for its number) before gate / up / down."""
     graph_safe = True
 
-    NAMES = dict(router="router", router_bias="router.b", expert="e{e}.", gate="gate", up="up", down="down")
+    NAMES = dict(router="router", router_bias="router.b", correction="correction", expert="e{e}.", gate="gate", up="up",
+                 down="down")
     TILE = 64                        # rows per block of the grouped product; an expert's run is padded to it
 
     def __init__(self, name: str, hidden_size: int, intermediate_size: int, num_experts: int, top: int,
-                 router_bias: bool = True, names: Optional[dict] = None):
+                 router_bias: bool = True, names: Optional[dict] = None, gated: bool = True, activation: str = "silu",
+                 routing: str = "top_logits", correction: bool = False, group_count: int = 1, group_keep: int = 1,
+                 identity: int = 0, weight_scale: float = 1.0):
         super().__init__(name, hidden_size=hidden_size, intermediate_size=intermediate_size, num_experts=num_experts, top=top,
-                         router_bias=router_bias)
+                         router_bias=router_bias, gated=gated, activation=activation, routing=routing, correction=correction,
+                         group_count=group_count, group_keep=group_keep, identity=identity, weight_scale=weight_scale)
         self.hidden, self.inter, self.E, self.top = int(hidden_size), int(intermediate_size), int(num_experts), int(top)
-        if not 1 <= self.top <= self.E or self.top > 32 or self.E > 256:
-            raise ValueError(f"mixture of experts: top {top} of {num_experts} experts is not supported (top <= 32, experts <= 256)")
-        self.has_bias = bool(router_bias)
+        self.identity = int(identity)
+        self.outputs = self.E + self.identity                     # what the router puts out
+        if self.E < 1 or self.identity < 0 or not 1 <= self.top <= self.outputs or self.top > 32 or self.outputs > 256:
+            raise ValueError(f"mixture of experts: top {top} of {num_experts} experts (+ {identity} identity experts) is not "
+                             f"supported (top <= 32, router outputs <= 256)")
+        if routing not in ("top_logits", "scores"):
+            raise ValueError(f"mixture of experts: routing must be \"top_logits\" or \"scores\", got {routing!r}")
+        if activation not in kernels.bindings.ACTIVATIONS or (gated and activation != "silu"):
+            raise ValueError(f"mixture of experts: activation {activation!r} is not supported" + (" by gated experts" if gated else ""))
+        self.gated, self.activation, self.routing = bool(gated), activation, routing
+        self.has_bias = bool(router_bias) and routing == "top_logits"
+        self.has_correction = bool(correction)
+        self.group_count, self.group_keep = max(1, int(group_count)), int(group_keep)
+        self.weight_scale = float(weight_scale)
+        if routing == "top_logits" and (self.identity or self.has_correction or self.group_count > 1 or self.weight_scale != 1.0):
+            raise ValueError("mixture of experts: identity experts, a correction, groups and a weight scale belong to routing=\"scores\"")
+        if self.group_count > 1:
+            if self.outputs % self.group_count or not 1 <= self.group_keep <= self.group_count:
+                raise ValueError(f"mixture of experts: {self.outputs} router outputs do not form {group_count} equal groups of "
+                                 f"which {group_keep} are kept")
+            if self.group_keep * (self.outputs // self.group_count) < self.top:
+                raise ValueError(f"mixture of experts: {group_keep} groups of {self.outputs // self.group_count} hold fewer than top = {top} experts")
         self.t = {**self.NAMES, **(names or {})}
 
     def _expert(self, e: int, role: str) -> str:
         return self.name + self.t["expert"].format(e=e) + self.t[role]
 
     def tensors(self):
-        specs = [TensorSpec(self.name + self.t["router"], (self.E, self.hidden))]
+        specs = [TensorSpec(self.name + self.t["router"], (self.outputs, self.hidden))]
         if self.has_bias:
             specs.append(TensorSpec(self.name + self.t["router_bias"], (self.E,), role="bias"))
+        if self.has_correction:
+            specs.append(TensorSpec(self.name + self.t["correction"], (self.outputs,), role="bias"))
         for e in range(self.E):
-            specs += [TensorSpec(self._expert(e, "gate"), (self.inter, self.hidden)),
-                      TensorSpec(self._expert(e, "up"), (self.inter, self.hidden)),
+            if self.gated:
+                specs.append(TensorSpec(self._expert(e, "gate"), (self.inter, self.hidden)))
+            specs += [TensorSpec(self._expert(e, "up"), (self.inter, self.hidden)),
                       TensorSpec(self._expert(e, "down"), (self.hidden, self.inter))]
         return specs
 
@@ -116,18 +151,23 @@ class MixtureOfExperts(Part):
         super().bind(get, runtime)
         self.router = get(self.name + self.t["router"]).to(torch.float32).contiguous()        # the router is float32 in both modes
         self.router_bias = get(self.name + self.t["router_bias"]).to(torch.float32).contiguous() if self.has_bias else None
-        # [E, 2*inter, hidden]: an expert's gate rows, then its up rows; [E, hidden, inter]
-        gates, ups = [get(self._expert(e, "gate")) for e in range(self.E)], [get(self._expert(e, "up")) for e in range(self.E)]
+        self.correction = get(self.name + self.t["correction"]).to(torch.float32).contiguous() if self.has_correction else None
+        # [E, 2*inter, hidden]: an expert's gate rows, then its up rows (ungated: [E, inter, hidden]); [E, hidden, inter]
+        ups = [get(self._expert(e, "up")) for e in range(self.E)]
         self.down = torch.stack([get(self._expert(e, "down")) for e in range(self.E)]).contiguous()
         # The tensor-core form (bfloat16 engine, sizes the tcgen05 product takes): an expert's gate and up rows alternate,
         # g0, u0, g1, u1, ..., so that SiLU(gate)·up is the product's epilogue, and runs are padded to its tiles of 128
         # rows.  Otherwise float32 multiply-adds on [gate; up] with tiles of 64 rows.
-        self.fused = (runtime.dtype == torch.bfloat16 and self.down.dtype == torch.bfloat16 and gates[0].dtype == torch.bfloat16
-                      and self.hidden % 16 == 0 and self.inter % 8 == 0)
-        if self.fused:
+        self.fused = (runtime.dtype == torch.bfloat16 and self.down.dtype == torch.bfloat16 and ups[0].dtype == torch.bfloat16
+                      and self.hidden % 16 == 0 and self.inter % (8 if self.gated else 16) == 0)
+        if not self.gated:
+            self.gate_up = torch.stack(ups).contiguous()
+        elif self.fused:
+            gates = [get(self._expert(e, "gate")) for e in range(self.E)]
             self.gate_up = torch.stack([torch.stack([g, u], dim=1).reshape(2 * self.inter, self.hidden)
                                         for g, u in zip(gates, ups)]).contiguous()
         else:
+            gates = [get(self._expert(e, "gate")) for e in range(self.E)]
             self.gate_up = torch.stack([torch.cat([g, u], dim=0) for g, u in zip(gates, ups)]).contiguous()
 
     def weight_bytes(self) -> int:
@@ -137,15 +177,19 @@ class MixtureOfExperts(Part):
 
     def flops_per_token(self) -> float:
         """Multiply-adds x 2 a token costs: the router and `top` experts."""
-        return 2.0 * (self.E * self.hidden + self.top * 3 * self.inter * self.hidden)
+        return 2.0 * (self.outputs * self.hidden + self.top * (3 if self.gated else 2) * self.inter * self.hidden)
 
     def route(self, h: torch.Tensor):
-        """(ids int32 [n, top], weights float32 [n, top])."""
+        """(ids int32 [n, top], weights float32 [n, top]); an id of `num_experts` or more names an identity expert."""
         rt = self.runtime
         n = h.shape[0]
         ids = rt.empty(n, self.top, dtype=torch.int32)
         weights = rt.empty(n, self.top, dtype=torch.float32)
-        kernels.moe_route(h, self.router_bias, self.top, ids, weights, router=self.router)       # logits, choice and weights in one kernel
+        if self.routing == "scores":
+            kernels.moe_route_scored(h, self.router, self.correction, self.top, self.group_count, self.group_keep,
+                                     self.weight_scale, ids, weights)
+        else:
+            kernels.moe_route(h, self.router_bias, self.top, ids, weights, router=self.router)   # logits, choice and weights in one kernel
         return ids, weights
 
     defers_sum = True         # forward(..., deferred=True) may leave the weighted sum of a token's rows to the caller
@@ -153,7 +197,8 @@ class MixtureOfExperts(Part):
     def forward(self, h: torch.Tensor, step=None, residual=None, deferred: bool = False):
         """The mixture's output float32 [n, hidden]; with `deferred`, instead the pieces of its last step, (rows float32
         [sorted rows, hidden], row_of int32 [n, top], weights float32 [n, top]), for a caller whose own kernel adds
-        sum_j weights[t, j] · rows[row_of[t, j]] into the stream (`kernels.scaled_add_experts`)."""
+        sum_j weights[t, j] · rows[row_of[t, j]] into the stream (`kernels.scaled_add_experts`, `kernels.group_norm`); a
+        negative row_of stands for the token's own input h (an identity expert)."""
         rt = self.runtime
         n = h.shape[0]
         ids, weights = self.route(h)
@@ -164,23 +209,25 @@ class MixtureOfExperts(Part):
         tile_expert = rt.empty(rows // tile, dtype=torch.int32)
         kernels.moe_plan(ids, self.E, tile, row_of, src_tok, tile_expert)
         y = rt.empty(rows, self.hidden, dtype=torch.float32)
-        out = rt.empty(n, self.hidden, dtype=torch.float32)
+        act = rt.empty(rows, self.inter)
         if self.fused:
             hs = rt.empty(rows, self.hidden)
             kernels.moe_gather(h, src_tok, hs)                       # the sorted rows, dense, as the product's TMA loads want them
-            act = rt.empty(rows, self.inter)
-            kernels.gemm_tcgen05_grouped(hs, self.gate_up, tile_expert, act, kernels.bindings.EPI_SILU_MUL, n_sms=rt.n_sms)
+            if self.gated:
+                kernels.gemm_tcgen05_grouped(hs, self.gate_up, tile_expert, act, kernels.bindings.EPI_SILU_MUL, n_sms=rt.n_sms)
+            else:
+                kernels.gemm_tcgen05_grouped(hs, self.gate_up, tile_expert, act, kernels.bindings.EPI_ACT[self.activation], n_sms=rt.n_sms)
             kernels.gemm_tcgen05_grouped(act, self.down, tile_expert, y, kernels.bindings.EPI_STORE, n_sms=rt.n_sms)
-            if deferred:
-                return y, row_of, weights
-            kernels.moe_combine(y, row_of, weights, out)
-            return out
-        gu = rt.empty(rows, 2 * self.inter)
-        kernels.grouped_linear(h, src_tok, self.gate_up, tile_expert, tile, gu)
-        act = rt.empty(rows, self.inter)
-        kernels.silu_mul(gu, act)
-        kernels.grouped_linear(act, None, self.down, tile_expert, tile, y)
+        else:
+            gu = rt.empty(rows, (2 if self.gated else 1) * self.inter)
+            kernels.grouped_linear(h, src_tok, self.gate_up, tile_expert, tile, gu)
+            if self.gated:
+                kernels.silu_mul(gu, act)
+            else:
+                kernels.activation(gu, self.activation, act)
+            kernels.grouped_linear(act, None, self.down, tile_expert, tile, y)
         if deferred:
             return y, row_of, weights
-        kernels.moe_combine(y, row_of, weights, out)
+        out = rt.empty(n, self.hidden, dtype=torch.float32)
+        kernels.moe_combine(y, row_of, weights, out, ident=h if self.identity else None)
         return out

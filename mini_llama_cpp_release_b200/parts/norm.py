@@ -85,3 +85,49 @@ class LayerNorm(Part):
         out = self.runtime.empty(*x.shape, dtype=copy_dtype) if copy_dtype is not None else None
         kernels.layernorm(x, y, self.gain, self.eps, out, of_branch=True)
         return out
+
+
+@register_part("norm", "rmsnorm_grouped")
+class GroupRMSNorm(Part):
+    """RMS norm in groups: the row is cut into `groups` equal consecutive parts, each divided by its own
+    sqrt(mean(part²) + eps), and the whole row is multiplied by the gain.  One group is the ordinary RMS norm.  Two
+    uses, as `LayerNorm` has: `forward`, the norm of the stream (adds `delta` first), and `renorm`, for arrangements
+    that put the norm behind the residual sum.  `tensor` is the gain's name below the part's prefix."""
+    graph_safe = True
+
+    def __init__(self, name: str, size: int, eps: float, groups: int = 1, tensor: str = "weight"):
+        super().__init__(name, size=size, eps=eps, groups=groups, tensor=tensor)
+        self.size, self.eps, self.groups = int(size), float(eps), int(groups)
+        if self.groups < 1 or self.size % self.groups:
+            raise ValueError(f"norm in groups: {size} entries do not split into {groups} equal groups")
+        self.tensor = self.name + tensor
+
+    def tensors(self):
+        return [TensorSpec(self.tensor, (self.size,), role="gain", init="one_plus_normal")]
+
+    def bind(self, get, runtime):
+        super().bind(get, runtime)
+        self.gain = get(self.tensor).to(torch.float32).contiguous()
+
+    def weight_bytes(self) -> int:
+        return self.gain.numel() * 4
+
+    def forward(self, x: torch.Tensor, delta: Optional[torch.Tensor] = None,
+                out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        """x: float32 [n, size], updated in place to x + delta when delta is given; returns the normed copy."""
+        if delta is not None:
+            x.add_(delta.sum(dim=0) if delta.dim() == 3 else delta)
+        out = self.runtime.empty(*x.shape, dtype=out_dtype or self.runtime.dtype)
+        kernels.group_norm(x, self.groups, self.gain, self.eps, out=out)
+        return out
+
+    def renorm(self, x: torch.Tensor, alpha: float, y: Optional[torch.Tensor] = None, expert_rows=None,
+               gate: Optional[torch.Tensor] = None, gate_col: int = 0, gate_bias: Optional[torch.Tensor] = None,
+               copy_dtype: Optional[torch.dtype] = None) -> Optional[torch.Tensor]:
+        """x (float32 [n, size], in place) <- norm(alpha · x + s * branch): the branch is `y` (float32 [n, size] or slices
+        that are added up) or `expert_rows` (see `kernels.group_norm`); s = sigmoid(gate columns + gate_bias) if a gate
+        is given, else one.  With `copy_dtype`, also returns the new x in that type (the next part's input)."""
+        out = self.runtime.empty(*x.shape, dtype=copy_dtype) if copy_dtype is not None else None
+        kernels.group_norm(x, self.groups, self.gain, self.eps, out=out, write_x=True, alpha=alpha, y=y, expert_rows=expert_rows,
+                           gate=gate, gate_col=gate_col, gate_bias=gate_bias)
+        return out

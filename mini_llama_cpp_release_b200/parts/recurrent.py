@@ -187,6 +187,91 @@ class GatedLinearAttention(Part):
         return self.o(act, torch.float32, partial_ok=True)
 
 
+@register_part("mixer", "forget_gate_attention")
+class ForgetGateAttention(Part):
+    """The forget-gate form of gated linear attention (the HGRN2 design): per head a matrix memory S [dim, vdim] whose rows
+    decay by a forget gate with a lower bound, and what a row takes in is scaled by the gate's complement; there is no key.
+
+        q = silu(W_q h)  (heads x dim);   v = W_v h  (heads x vdim)
+        f = l + (1 - l) · sigmoid(W_f h + b_f)           (heads x dim; l the stored lower bound per channel)
+        S_t = diag(f_t) S_{t-1} + (1 - f_t) v_tᵀ;   o_t = S_tᵀ q_t                (no further scale)
+        out = W_o ( o / rms(o) · w_norm )                 (rms over vdim per head, w_norm shared by the heads)
+
+    State per sequence: S for every head, float32, zero at the start.  Gates, their complements, silu(q) and the whole
+    recurrence are float32 in both engine modes.  The walk over tokens is the one of `GatedLinearAttention`, with decay f,
+    key 1 - f and query silu(z_q).  Without a lower-bound tensor (`lower_bound=False`) l = 0; `gate_bias=False`: no b_f.
+    Offers `in_weights()`, `in_width()`, `mix()` and `o` to an arrangement that computes other matrices on the same input
+    in the mixer's input product.  `names`: the tensors' names below the part's prefix, by role."""
+    graph_safe = True
+
+    NAMES = dict(q="q", f="f", f_bias="f.b", lower="lower", v="v", o="o", norm="norm")
+
+    def __init__(self, name: str, hidden_size: int, num_heads: int, head_dim: int, v_head_dim: int, norm_eps: float,
+                 lower_bound: bool = True, gate_bias: bool = True, names: Optional[dict] = None):
+        super().__init__(name, hidden_size=hidden_size, num_heads=num_heads, head_dim=head_dim, v_head_dim=v_head_dim,
+                         norm_eps=norm_eps, lower_bound=lower_bound, gate_bias=gate_bias)
+        if not 1 <= head_dim <= 256:
+            raise ValueError(f"forget-gate linear attention: key sizes up to 256 are supported, got {head_dim}")
+        self.hidden, self.H, self.dim, self.vdim = int(hidden_size), int(num_heads), int(head_dim), int(v_head_dim)
+        self.eps = float(norm_eps)
+        self.has_lower, self.has_bias = bool(lower_bound), bool(gate_bias)
+        self.t = {role: name + n for role, n in {**self.NAMES, **(names or {})}.items()}
+        self.n_qk, self.n_v = self.H * self.dim, self.H * self.vdim
+
+    def tensors(self):
+        t, hid = self.t, self.hidden
+        specs = [TensorSpec(t["q"], (self.n_qk, hid)), TensorSpec(t["f"], (self.n_qk, hid)), TensorSpec(t["v"], (self.n_v, hid)),
+                 TensorSpec(t["o"], (hid, self.n_v)), TensorSpec(t["norm"], (self.vdim,), role="gain", init="one_plus_normal")]
+        if self.has_bias:
+            specs.append(TensorSpec(t["f_bias"], (self.n_qk,), role="bias"))
+        if self.has_lower:
+            specs.append(TensorSpec(t["lower"], (self.n_qk,), role="bias", init="unit_interval"))
+        return specs
+
+    def cache_need(self):
+        return None
+
+    def state_spec(self) -> StateSpec:
+        return StateSpec((self.H * self.vdim * self.dim,), torch.float32)
+
+    def bind(self, get, runtime):
+        super().bind(get, runtime)
+        t = self.t
+        self._in = [get(t[r]) for r in ("q", "f", "v")]          # columns of the input product: q | f | v
+        self.in_proj: Optional[Linear] = None
+        self.f_bias = _f32(get(t["f_bias"])) if self.has_bias else None
+        self.lower = _f32(get(t["lower"])) if self.has_lower else None
+        self.gain = _f32(get(t["norm"]))
+        self.o = Linear(get(t["o"]), runtime)
+
+    def in_weights(self):
+        return list(self._in)
+
+    def in_width(self) -> int:
+        return 2 * self.n_qk + self.n_v
+
+    def weight_bytes(self) -> int:
+        return sum(w.numel() * w.element_size() for w in self._in) + self.o.nbytes()
+
+    def mix(self, proj: torch.Tensor, col: int, step, memory: MixerMemory) -> torch.Tensor:
+        """From the float32 projection rows `proj`, whose columns from `col` on are [q | f | v]: the normed heads
+        [n, heads·vdim] in the engine's type, the input of `self.o`."""
+        rt = self.runtime
+        n = proj.shape[0]
+        # partial outputs, one slice per slab of the state's rows; the head norm adds them up as it reads them
+        o = rt.empty(kernels.gla_slices(step.n_seqs, self.H, self.dim, self.vdim, rt.device), n, self.n_v, dtype=torch.float32)
+        kernels.forget_gate_attention(proj, col, col + self.n_qk, col + 2 * self.n_qk, self.f_bias, self.lower, memory.state,
+                                      step, self.H, self.dim, self.vdim, o)
+        act = rt.empty(n, self.n_v)
+        kernels.gated_rmsnorm(o, None, 0, self.gain, self.eps, self.H, self.vdim, act)
+        return act
+
+    def forward(self, h: torch.Tensor, step, memory: MixerMemory) -> torch.Tensor:
+        if self.in_proj is None:
+            self.in_proj = fused_rows(self._in, self.runtime)
+        return self.o(self.mix(self.in_proj(h, torch.float32), 0, step, memory), torch.float32, partial_ok=True)
+
+
 @register_part("mixer", "gated_linear_recurrence")
 class GatedLinearRecurrence(Part):
     """The recurrent block of Griffin (De et al., "Griffin: Mixing Gated Linear Recurrences with Local Attention for

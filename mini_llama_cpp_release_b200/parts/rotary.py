@@ -135,8 +135,10 @@ def stretched_frequencies(dims: int, base: float, scaling: Optional[dict]) -> Tu
 
 @register_part("position", "rope_partial")
 class RopePartial(Part):
-    """Rotate-half rotation of the first `dims` entries of each head (the rest pass unchanged), with optional
-    stretching of the frequencies (`stretched_frequencies`).  The model gives no largest position, so the table
+    """Rotation of the first `dims` entries of each head (the rest pass unchanged), with optional stretching of the
+    frequencies (`stretched_frequencies`).  `pairing` says which entries form a pair: "half" pairs entry i with i + dims/2
+    (rotate-half), "interleaved" pairs entry 2i with 2i + 1; the pair (u, v) becomes (u cos a - v sin a, v cos a + u sin a)
+    with a = position · f_i either way, so the table is the same and only the mixer's kernel reads `interleaved`.  The model gives no largest position, so the table
     [positions][dims/2] of (cos, sin) grows: it is rebuilt, twice as long, when a step reaches beyond it.  Tables
     once handed out stay alive and valid for the positions they hold, so a captured graph that reads one keeps
     reading the same memory; a step is captured for a bound on its positions and asks for its table with that bound."""
@@ -145,8 +147,13 @@ class RopePartial(Part):
 
     MIN_POSITIONS = 4096
 
-    def __init__(self, name: str, dims: int, base: float, scaling: Optional[dict] = None):
-        super().__init__(name, dims=dims, base=base, scaling=scaling)
+    PAIRINGS = ("half", "interleaved")
+
+    def __init__(self, name: str, dims: int, base: float, scaling: Optional[dict] = None, pairing: str = "half"):
+        super().__init__(name, dims=dims, base=base, scaling=scaling, pairing=pairing)
+        if pairing not in self.PAIRINGS:
+            raise ValueError(f"rope: pairing must be one of {', '.join(self.PAIRINGS)}; got {pairing!r}")
+        self.interleaved = pairing == "interleaved"
         if dims < 0 or dims % 2:
             raise ValueError(f"rope: the rotated size must be even and not negative, got {dims}")
         if not math.isfinite(base) or base <= 0:

@@ -32,6 +32,8 @@ def random_tensor(spec: TensorSpec, seed: int, dtype: torch.dtype, std: float = 
     g = torch.Generator(device="cpu")
     g.manual_seed(tensor_seed(seed, spec.name))
     shape = spec.default_shape if (spec.default_shape is not None and -1 in tuple(spec.shape)) else spec.shape
+    if spec.init == "unit_interval":                  # a bound or a rate that lies between 0 and 1
+        return (torch.rand(tuple(shape), generator=g, dtype=torch.float32) * 0.9 + 0.05).to(dtype)
     t = torch.randn(tuple(shape), generator=g, dtype=torch.float32) * std
     if spec.init == "one_plus_normal":
         t = t + 1.0
