@@ -4,6 +4,7 @@
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L] [--config NAME] [--dtype bfloat16|float32]
     python bench.py --impl reference      # the reference project's own GPU path on the same work
     python bench.py --compare mepolix-w896 [--layers 6]   # the Mepolix (or, kebesun-w896, the Kebesun) design beside Qwen2 at equal sizes (a line of its own)
+    python bench.py --compare lonulix-w896 [--layers 6]   # the Lonulix design beside Kebesun layers of the same mixers and sizes
 
 A "step" is one decode step of the whole batch.  The default run (`--config qwen2-0.5b`) has the layer sizes of a
 Qwen2-0.5B (24 layers, width 896, 14 query heads on 2 kv heads of size 64, feed-forward 4864, vocabulary 151936,
@@ -45,7 +46,9 @@ CONFIGS = {
 }
 # a Mepolix preset → the Qwen2 preset it is timed beside (equal width, attention shape, feed-forward and vocabulary)
 COMPARE = {"mepolix-w896": "qwen2-0.5b", "mepolix-w1536": "qwen2-1.5b", "mepolix-w3584": "qwen2-7b",
-           "kebesun-w896": "qwen2-0.5b", "kebesun-w1536": "qwen2-1.5b", "kebesun-w3584": "qwen2-7b"}
+           "kebesun-w896": "qwen2-0.5b", "kebesun-w1536": "qwen2-1.5b", "kebesun-w3584": "qwen2-7b",
+           # a Lonulix preset → the Kebesun layers of the same mixers, sizes and order (its closest design)
+           "lonulix-w896": "kebesun-lg-w896", "lonulix-w1536": "kebesun-lg-w1536", "lonulix-w3584": "kebesun-lg-w3584"}
 REF_DIR = os.path.join(ROOT, "baseline", "_ref")
 REF_SOURCE = os.environ.get("MLC_REFERENCE_SOURCE", "/root/reference")     # where the reference's checkout lies, if baseline/_ref is empty
 REF_PREFILL_TOKENS = 32
@@ -146,10 +149,10 @@ def compare(args) -> int:
     steps, warmup = max(1, min(args.steps, 512)), max(3, args.warmup)
     out = {"compare": args.compare, "layers": layers, "batch": batch, "prompt_len": prompt_len, "dtype": args.dtype,
            "peaks": pk["source"]}
-    for label, preset in ((args.compare.split("-")[0], args.compare), ("qwen2", COMPARE[args.compare])):
+    for label, preset in ((args.compare.split("-")[0], args.compare), (COMPARE[args.compare].split("-")[0], COMPARE[args.compare])):
         raw = dict(measure.PRESETS[preset])
         if "layers" in raw:
-            # Mepolix: the last layers (they end on attention beside the recurrence); Kebesun: the first, one whole cycle
+            # Mepolix: the last layers (they end on attention beside the recurrence); the others: the first, whole cycles
             raw["layers"] = raw["layers"][-layers:] if raw.get("architecture") == "Mepolix" else raw["layers"][:layers]
         else:
             raw["num_hidden_layers"] = layers
@@ -191,8 +194,9 @@ def main() -> int:
                     help="run one part only and print a short line (for profiling a small case)")
     ap.add_argument("--prompt-len", type=int, default=None, help="prompt length of the --only runs")
     ap.add_argument("--compare", default=None, choices=sorted(COMPARE),
-                    help="instead of the benchmark line: prompt and decode throughput of a Mepolix or Kebesun preset beside the Qwen2 "
-                         "preset of the same width, head shape and feed-forward, at --layers layers each (default 6)")
+                    help="instead of the benchmark line: prompt and decode throughput of a Mepolix, Kebesun or Lonulix preset beside the "
+                         "preset of its closest design at the same width, head shape and feed-forward, at --layers layers each "
+                         "(default 6)")
     args = ap.parse_args()
     if args.compare:
         return compare(args)

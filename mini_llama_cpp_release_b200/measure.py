@@ -59,6 +59,33 @@ def _kebesun(width: int, ff: int, heads: int, kv_heads: int, head: int, n_layers
             "layers": [{"type": t, "mixer": dict(m), "mlp": dict(f)} for t, m, f in (cycle[i % 6] for i in range(n_layers))]}
 
 
+def _lonulix(width: int, ff: int, heads: int, head: int, n_layers: int, vocab: int, design: str = "Lonulix") -> Dict[str, Any]:
+    """Lonulix layers of real width in a cycle of four: latent attention with the dense feed-forward, forget-gate linear
+    attention with experts, latent attention with experts, forget-gate linear attention with the dense feed-forward.  The
+    width, the head count and head size and the dense feed-forward are the Qwen2 preset's of the same width; the latent
+    rows (80 + 48 rotated), the linear attention's shape (half the heads, values twice as wide) and the experts (eight of
+    half the dense size, two chosen) are the Kebesun preset's, so that like kernels can be timed side by side.
+    `design="Kebesun"` gives that design's layers of the same mixers and sizes in the same order (latent attention without
+    the query latent and the window, gated linear attention for the forget-gate form, gated experts without groups and
+    identity experts): the model the Lonulix preset is timed beside."""
+    rot = {"dims": 48, "base": 1000000.0}
+    lat = {"heads": heads, "dim": head, "rot_dim": 48, "vdim": head, "kv_rank": 80, "scale": (head + 48) ** -0.5, "rot": rot}
+    lin = {"heads": max(1, heads // 2), "dim": head, "vdim": 2 * head}
+    dense = {"kind": "dense", "ff": ff}
+    if design == "Kebesun":
+        lin, kind = dict(lin, tau=16.0), "gla"
+        moe = {"kind": "moe", "expert": {"ff": ff // 2}, "router": {"experts": 8, "top": 2}}
+        top = {"architecture": "Kebesun", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}}
+    else:
+        lat, kind = dict(lat, q_rank=max(64, width // 4), mask={"size": 1024}), "hgrn2"
+        moe = {"kind": "moe", "expert": {"ff": ff // 2},
+               "router": {"experts": 8, "top": 2, "identity": 2, "scale": 2.5, "groups": {"count": 5, "keep": 3}}}
+        top = {"architecture": "Lonulix", "vocab": vocab, "width": width, "norm": {"eps": 1e-6, "groups": 4},
+               "postln_alpha": 1.5, "embedding": {"scale": 2.0}}
+    cycle = [("latent_attention", lat, dense), (kind, lin, moe), ("latent_attention", lat, moe), (kind, lin, dense)]
+    return dict(top, layers=[{"type": t, "mixer": dict(m), "mlp": dict(f)} for t, m, f in (cycle[i % 4] for i in range(n_layers))])
+
+
 PRESETS: Dict[str, Dict[str, Any]] = {
     "tiny-a": dict(_QWEN2, hidden_size=64, intermediate_size=176, num_hidden_layers=2, num_attention_heads=4,
                    num_key_value_heads=2, head_dim=16, vocab_size=512, max_position_embeddings=256, rope_theta=10000.0,
@@ -83,6 +110,13 @@ PRESETS: Dict[str, Dict[str, Any]] = {
     "kebesun-w896": _kebesun(896, 4864, 14, 2, 64, 24, 151936),
     "kebesun-w1536": _kebesun(1536, 8960, 12, 2, 128, 24, 151936),
     "kebesun-w3584": _kebesun(3584, 18944, 28, 4, 128, 24, 152064),
+    # the Lonulix design at the same widths, and the Kebesun layers of the same mixers it is timed beside (see `_lonulix`)
+    "lonulix-w896": _lonulix(896, 4864, 14, 64, 24, 151936),
+    "lonulix-w1536": _lonulix(1536, 8960, 12, 128, 24, 151936),
+    "lonulix-w3584": _lonulix(3584, 18944, 28, 128, 24, 152064),
+    "kebesun-lg-w896": _lonulix(896, 4864, 14, 64, 24, 151936, design="Kebesun"),
+    "kebesun-lg-w1536": _lonulix(1536, 8960, 12, 128, 24, 151936, design="Kebesun"),
+    "kebesun-lg-w3584": _lonulix(3584, 18944, 28, 128, 24, 152064, design="Kebesun"),
 }
 
 FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0)
