@@ -12,7 +12,9 @@
 //
 // Everything is float32.  A block per row: the row's v is staged in shared memory, then every group is summed by a fixed
 // set of warps (a group's warps add their parts in a fixed order), so a row's result does not depend on what else is in
-// the step.
+// the step.  Two forms of the same arithmetic: `group_norm_kernel<4>` moves four neighbouring entries per access (16-byte
+// loads of every operand issued before any is used; rows, strides and parts that are multiples of four entries on
+// 16-byte boundaries), `group_norm_kernel<1>` takes every other size one entry at a time.
 #include "common.cuh"
 
 namespace mlc {
@@ -40,44 +42,137 @@ struct GroupNormArgs {
     int out_dtype;
 };
 
+// V entries of one operand at element offset `at`.
+template <int V> struct Pack { float e[V]; };
+
+template <int V>
+__device__ __forceinline__ Pack<V> load_pack(const float* p, long long at) {
+    Pack<V> r;
+    if constexpr (V == 4) {
+        const float4 q = *reinterpret_cast<const float4*>(p + at);
+        r.e[0] = q.x; r.e[1] = q.y; r.e[2] = q.z; r.e[3] = q.w;
+    } else {
+        r.e[0] = p[at];
+    }
+    return r;
+}
+
+template <int V>
+__device__ __forceinline__ Pack<V> load_pack_any(const void* p, int dtype, long long at) {
+    if (dtype == MLC_DTYPE_F32) return load_pack<V>((const float*)p, at);
+    Pack<V> r;
+    if constexpr (V == 4) {
+        const uint2 q = *reinterpret_cast<const uint2*>((const bf16*)p + at);
+        const bf16* h = reinterpret_cast<const bf16*>(&q);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) r.e[k] = to_float(h[k]);
+    } else {
+        r.e[0] = to_float(((const bf16*)p)[at]);
+    }
+    return r;
+}
+
+template <int V>
+__device__ __forceinline__ void store_pack(const Pack<V>& r, float* xw, void* out, int out_dtype, long long x_at, long long out_at) {
+    if constexpr (V == 4) {
+        if (xw != nullptr) *reinterpret_cast<float4*>(xw + x_at) = make_float4(r.e[0], r.e[1], r.e[2], r.e[3]);
+        if (out != nullptr) {
+            if (out_dtype == MLC_DTYPE_F32) {
+                *reinterpret_cast<float4*>((float*)out + out_at) = make_float4(r.e[0], r.e[1], r.e[2], r.e[3]);
+            } else {
+                uint2 q;
+                bf16* h = reinterpret_cast<bf16*>(&q);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) h[k] = from_float<bf16>(r.e[k]);
+                *reinterpret_cast<uint2*>((bf16*)out + out_at) = q;
+            }
+        }
+    } else {
+        if (xw != nullptr) xw[x_at] = r.e[0];
+        if (out != nullptr) {
+            if (out_dtype == MLC_DTYPE_F32) ((float*)out)[out_at] = r.e[0];
+            else ((bf16*)out)[out_at] = from_float<bf16>(r.e[0]);
+        }
+    }
+}
+
+constexpr int GN_MAX_TOP = 8;        // a token's expert rows loaded side by side; more are taken in rounds of this many
+
+template <int V>
 __global__ void group_norm_kernel(GroupNormArgs a) {
-    extern __shared__ float v[];                      // [d]
+    extern __shared__ __align__(16) float v[];        // [d]
     __shared__ float part[32];
     const int t = blockIdx.x;
     const int d = a.d;
     const float* xr = a.x + (long long)t * a.x_stride;
     const bool has_branch = a.y != nullptr || a.rows != nullptr;
-    for (int i = threadIdx.x; i < d; i += blockDim.x) {
-        float val = xr[i];
+    for (int i = threadIdx.x * V; i < d; i += blockDim.x * V) {
+        Pack<V> val = load_pack<V>(xr, i);
         if (has_branch) {
-            float b = 0.0f;
+            Pack<V> b, zz, zb;
+            const bool gated = a.z != nullptr;
+            if (gated) {                               // the gate's operands first: their loads overlap the branch's
+                zz = load_pack<V>(a.z, (long long)t * a.z_stride + i);
+                if (a.z_bias != nullptr) zb = load_pack<V>(a.z_bias, i);
+            }
+#pragma unroll
+            for (int k = 0; k < V; ++k) b.e[k] = 0.0f;
             if (a.y != nullptr) {
-                for (int s = 0; s < a.slices; ++s) b += a.y[((long long)s * a.n + t) * d + i];
+                int s = 0;
+                for (; s + 4 <= a.slices; s += 4) {    // four slices' loads in flight, added in slice order
+                    Pack<V> p[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) p[u] = load_pack<V>(a.y, ((long long)(s + u) * a.n + t) * d + i);
+#pragma unroll
+                    for (int u = 0; u < 4; ++u)
+#pragma unroll
+                        for (int k = 0; k < V; ++k) b.e[k] += p[u].e[k];
+                }
+                for (; s < a.slices; ++s) {
+                    const Pack<V> p = load_pack<V>(a.y, ((long long)s * a.n + t) * d + i);
+#pragma unroll
+                    for (int k = 0; k < V; ++k) b.e[k] += p.e[k];
+                }
             } else {
-                for (int j = 0; j < a.top; ++j) {
-                    const int r = a.row_of[(long long)t * a.top + j];
-                    float e;
-                    if (r >= 0) e = a.rows[(long long)r * d + i];
-                    else if (a.ident == nullptr) e = 0.0f;
-                    else e = a.ident_dtype == MLC_DTYPE_F32 ? ((const float*)a.ident)[(long long)t * d + i]
-                                                            : to_float(((const bf16*)a.ident)[(long long)t * d + i]);
-                    b = fmaf(a.weights[(long long)t * a.top + j], e, b);
+                for (int j0 = 0; j0 < a.top; j0 += GN_MAX_TOP) {
+                    Pack<V> p[GN_MAX_TOP];
+                    float w[GN_MAX_TOP];
+#pragma unroll
+                    for (int u = 0; u < GN_MAX_TOP; ++u) {
+                        const int j = j0 + u;
+                        w[u] = 0.0f;
+#pragma unroll
+                        for (int k = 0; k < V; ++k) p[u].e[k] = 0.0f;
+                        if (j < a.top) {
+                            const int r = a.row_of[(long long)t * a.top + j];
+                            w[u] = a.weights[(long long)t * a.top + j];
+                            if (r >= 0) p[u] = load_pack<V>(a.rows, (long long)r * d + i);
+                            else if (a.ident != nullptr) p[u] = load_pack_any<V>(a.ident, a.ident_dtype, (long long)t * d + i);
+                        }
+                    }
+#pragma unroll
+                    for (int u = 0; u < GN_MAX_TOP; ++u)
+                        if (j0 + u < a.top)
+#pragma unroll
+                            for (int k = 0; k < V; ++k) b.e[k] = fmaf(w[u], p[u].e[k], b.e[k]);
                 }
             }
-            if (a.z != nullptr) {
-                const float zz = a.z[(long long)t * a.z_stride + i] + (a.z_bias != nullptr ? a.z_bias[i] : 0.0f);
-                b *= 1.0f / (1.0f + expf(-zz));
+#pragma unroll
+            for (int k = 0; k < V; ++k) {
+                float bk = b.e[k];
+                if (gated) bk *= 1.0f / (1.0f + expf(-(zz.e[k] + (a.z_bias != nullptr ? zb.e[k] : 0.0f))));
+                val.e[k] = fmaf(a.alpha, val.e[k], bk);
             }
-            val = fmaf(a.alpha, val, b);
         }
-        v[i] = val;
+#pragma unroll
+        for (int k = 0; k < V; ++k) v[i + k] = val.e[k];
     }
     __syncthreads();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
     const int gsize = d / a.groups;
     int wpg = n_warps / a.groups;                     // warps that share a group
     if (wpg < 1) wpg = 1;
-    while (wpg > 1 && (wpg - 1) * 32 >= gsize) --wpg; // no warp without entries
+    while (wpg > 1 && (wpg - 1) * 32 * V >= gsize) --wpg; // no warp without entries
     const int at_once = n_warps / wpg;                // groups handled side by side
     const int sub = warp % wpg, team = warp / wpg;
     for (int g0 = 0; g0 < a.groups; g0 += at_once) {
@@ -85,9 +180,12 @@ __global__ void group_norm_kernel(GroupNormArgs a) {
         const bool live = team < at_once && g < a.groups;
         float ss = 0.0f;
         if (live)
-            for (int j = sub * 32 + lane; j < gsize; j += wpg * 32) {
-                const float e = v[g * gsize + j];
-                ss = fmaf(e, e, ss);
+            for (int j = (sub * 32 + lane) * V; j < gsize; j += wpg * 32 * V) {
+#pragma unroll
+                for (int k = 0; k < V; ++k) {
+                    const float e = v[g * gsize + j + k];
+                    ss = fmaf(e, e, ss);
+                }
             }
         ss = warp_sum(ss);
         __syncthreads();
@@ -97,14 +195,13 @@ __global__ void group_norm_kernel(GroupNormArgs a) {
             float total = 0.0f;
             for (int k = 0; k < wpg; ++k) total += part[team * wpg + k];
             const float f = 1.0f / sqrtf(total / (float)gsize + a.eps);
-            for (int j = sub * 32 + lane; j < gsize; j += wpg * 32) {
+            for (int j = (sub * 32 + lane) * V; j < gsize; j += wpg * 32 * V) {
                 const int i = g * gsize + j;
-                const float r = v[i] * f * a.gain[i % a.gain_len];
-                if (a.write_x) a.x[(long long)t * a.x_stride + i] = r;
-                if (a.out != nullptr) {
-                    if (a.out_dtype == MLC_DTYPE_F32) ((float*)a.out)[(long long)t * d + i] = r;
-                    else ((bf16*)a.out)[(long long)t * d + i] = from_float<bf16>(r);
-                }
+                const Pack<V> gn = load_pack<V>(a.gain, i % a.gain_len);
+                Pack<V> r;
+#pragma unroll
+                for (int k = 0; k < V; ++k) r.e[k] = v[i + k] * f * gn.e[k];
+                store_pack<V>(r, a.write_x ? a.x : nullptr, a.out, a.out_dtype, (long long)t * a.x_stride + i, (long long)t * d + i);
             }
         }
     }
@@ -139,8 +236,19 @@ extern "C" int mlc_group_norm(float* x, long long x_stride, int n, int d, int gr
     if (ident != nullptr && ident_dtype != MLC_DTYPE_F32 && ident_dtype != MLC_DTYPE_BF16) return MLC_ERR_BAD_DTYPE;
     GroupNormArgs a{x, x_stride, n, d, groups, gain, gain_len, eps, alpha, y, slices, rows, row_of, weights, top, ident,
                     ident_dtype, z, z_stride, z_bias, write_x, out, out_dtype};
-    const int threads = d <= 256 ? 64 : (d <= 1024 ? 128 : 256);
-    group_norm_kernel<<<n, threads, (size_t)d * sizeof(float), (cudaStream_t)stream>>>(a);
+    const int gsize = d / groups;
+    auto aligned = [](const void* p) { return p == nullptr || (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    const bool by_four = gsize % 4 == 0 && gain_len % 4 == 0 && x_stride % 4 == 0 && (z == nullptr || z_stride % 4 == 0) &&
+                         aligned(x) && aligned(gain) && aligned(y) && aligned(rows) && aligned(ident) && aligned(z) &&
+                         aligned(z_bias) && aligned(out);
+    if (by_four) {
+        int threads = ((d / 4 + 31) / 32) * 32;        // a thread per four entries, up to 512 threads a row
+        threads = threads < 64 ? 64 : (threads > 512 ? 512 : threads);
+        group_norm_kernel<4><<<n, threads, (size_t)d * sizeof(float), (cudaStream_t)stream>>>(a);
+    } else {
+        const int threads = d <= 256 ? 64 : (d <= 1024 ? 128 : 256);
+        group_norm_kernel<1><<<n, threads, (size_t)d * sizeof(float), (cudaStream_t)stream>>>(a);
+    }
     MLC_LAUNCH_CHECK();
     return 0;
 }

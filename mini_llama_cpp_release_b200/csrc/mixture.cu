@@ -34,11 +34,22 @@ __device__ __forceinline__ void route_logits(const TX* __restrict__ x, const flo
         float acc[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
+        if (e0 + 8 <= E) {
 #pragma unroll 4
-        for (int k = threadIdx.x; k < K; k += 128) {
-            const float xv = to_float(row[k]);
+            for (int k = threadIdx.x; k < K; k += 128) {
+                const float xv = to_float(row[k]);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) acc[j] = fmaf(xv, __ldg(w + (long long)min(e0 + j, E - 1) * K + k), acc[j]);
+                for (int j = 0; j < 8; ++j) acc[j] = fmaf(xv, __ldg(w + (long long)(e0 + j) * K + k), acc[j]);
+            }
+        } else {                                       // the last round of fewer than eight: only its own rows are read
+            const int live = E - e0;
+#pragma unroll 4
+            for (int k = threadIdx.x; k < K; k += 128) {
+                const float xv = to_float(row[k]);
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    if (j < live) acc[j] = fmaf(xv, __ldg(w + (long long)(e0 + j) * K + k), acc[j]);
+            }
         }
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
