@@ -22,42 +22,42 @@ constexpr int ROUTE_MAX_PER_LANE = 8;          // E <= 256
 // x · wᵀ + bias in float32 (w float32 [E][K]): eight experts at a time, every thread a strided share of K, partial sums
 // added within warps and then across them in a fixed order.  Without `w`, `x` holds the logits themselves, float32 [n][E].
 // Warp 0 then chooses: lane l keeps logits l, l + 32, ...
-// Router logits of token t into shared `logit[E]`: x · wᵀ + bias in float32 (w float32 [E][K]), eight experts at a time,
-// every thread a strided share of K, partial sums added within warps and then across them in a fixed order.  All 128
+// Router logits of token t into shared `logit[E]`: x · wᵀ + bias in float32 (w float32 [E][K]), eight or sixteen experts at a
+// time, every thread a strided share of K, partial sums added within warps and then across them in a fixed order.  All 128
 // threads of the block call it.
-template <typename TX>
-__device__ __forceinline__ void route_logits(const TX* __restrict__ x, const float* __restrict__ w, const float* __restrict__ bias,
-                                             int t, int E, int K, float (*part)[8], float* logit) {
+template <typename TX, int R>
+__device__ __forceinline__ void route_logits_by(const TX* __restrict__ x, const float* __restrict__ w, const float* __restrict__ bias,
+                                                int t, int E, int K, float (*part)[16], float* logit) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const TX* row = x + (long long)t * K;
-    for (int e0 = 0; e0 < E; e0 += 8) {
-        float acc[8];
+    for (int e0 = 0; e0 < E; e0 += R) {
+        float acc[R];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
-        if (e0 + 8 <= E) {
+        for (int j = 0; j < R; ++j) acc[j] = 0.0f;
+        if (e0 + R <= E) {
 #pragma unroll 4
             for (int k = threadIdx.x; k < K; k += 128) {
                 const float xv = to_float(row[k]);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) acc[j] = fmaf(xv, __ldg(w + (long long)(e0 + j) * K + k), acc[j]);
+                for (int j = 0; j < R; ++j) acc[j] = fmaf(xv, __ldg(w + (long long)(e0 + j) * K + k), acc[j]);
             }
-        } else {                                       // the last round of fewer than eight: only its own rows are read
+        } else {                                       // the last round of fewer than R: only its own rows are read
             const int live = E - e0;
 #pragma unroll 4
             for (int k = threadIdx.x; k < K; k += 128) {
                 const float xv = to_float(row[k]);
 #pragma unroll
-                for (int j = 0; j < 8; ++j)
+                for (int j = 0; j < R; ++j)
                     if (j < live) acc[j] = fmaf(xv, __ldg(w + (long long)(e0 + j) * K + k), acc[j]);
             }
         }
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
+        for (int j = 0; j < R; ++j) {
             const float v = warp_sum(acc[j]);
             if (lane == 0) part[warp][j] = v;
         }
         __syncthreads();
-        if (threadIdx.x < 8 && e0 + threadIdx.x < E) {
+        if (threadIdx.x < R && e0 + threadIdx.x < E) {
             const int e = e0 + threadIdx.x;
             logit[e] = ((part[0][threadIdx.x] + part[1][threadIdx.x]) + (part[2][threadIdx.x] + part[3][threadIdx.x]))
                        + (bias != nullptr ? bias[e] : 0.0f);
@@ -66,13 +66,22 @@ __device__ __forceinline__ void route_logits(const TX* __restrict__ x, const flo
     }
 }
 
+// Up to eight router outputs take one round of eight; more go sixteen at a time (ten outputs: one round, not two).  An
+// output's sum is formed in the same order either way.
+template <typename TX>
+__device__ __forceinline__ void route_logits(const TX* __restrict__ x, const float* __restrict__ w, const float* __restrict__ bias,
+                                             int t, int E, int K, float (*part)[16], float* logit) {
+    if (E <= 8) route_logits_by<TX, 8>(x, w, bias, t, E, K, part, logit);
+    else route_logits_by<TX, 16>(x, w, bias, t, E, K, part, logit);
+}
+
 template <typename TX>
 __global__ void __launch_bounds__(128)
 moe_route_kernel(const TX* __restrict__ x, const float* __restrict__ w, const float* __restrict__ bias, int n,
                  int E, int K, int top, int* __restrict__ ids, float* __restrict__ weights) {
     const int t = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    __shared__ float part[4][8];
+    __shared__ float part[4][16];
     __shared__ float logit[32 * ROUTE_MAX_PER_LANE];
     if (w != nullptr) route_logits<TX>(x, w, bias, t, E, K, part, logit);
     if (warp != 0) return;
@@ -135,7 +144,7 @@ moe_route_scored_kernel(const TX* __restrict__ x, const float* __restrict__ w, c
                         float* __restrict__ weights) {
     const int t = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    __shared__ float part[4][8];
+    __shared__ float part[4][16];
     __shared__ float logit[32 * ROUTE_MAX_PER_LANE];
     __shared__ float prob[32 * ROUTE_MAX_PER_LANE];
     __shared__ float gscore[32 * ROUTE_MAX_PER_LANE];
