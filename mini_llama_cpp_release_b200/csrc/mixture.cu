@@ -19,12 +19,12 @@ namespace mlc {
 constexpr int ROUTE_MAX_PER_LANE = 8;          // E <= 256
 
 // A block of four warps per token.  With `w` given, `x` is the branch's input [n][K] (TX) and the logits are
-// x · wᵀ + bias in float32 (w float32 [E][K]): eight experts at a time, every thread a strided share of K, partial sums
-// added within warps and then across them in a fixed order.  Without `w`, `x` holds the logits themselves, float32 [n][E].
+// x · wᵀ + bias in float32 (w float32 [E][K]; `route_logits` below).  Without `w`, `x` holds the logits themselves, float32 [n][E].
 // Warp 0 then chooses: lane l keeps logits l, l + 32, ...
-// Router logits of token t into shared `logit[E]`: x · wᵀ + bias in float32 (w float32 [E][K]), eight or sixteen experts at a
-// time, every thread a strided share of K, partial sums added within warps and then across them in a fixed order.  All 128
-// threads of the block call it.
+// Router logits of token t into shared `logit[E]`: x · wᵀ + bias in float32 (w float32 [E][K]), R outputs a round, every
+// thread a strided share of K, partial sums added within warps and then across them in a fixed order.  A round that has
+// fewer than R outputs left reads its last row again in their place and drops those sums (no branch around the loads:
+// all of a round's loads are in flight together).  All 128 threads of the block call it.
 template <typename TX, int R>
 __device__ __forceinline__ void route_logits_by(const TX* __restrict__ x, const float* __restrict__ w, const float* __restrict__ bias,
                                                 int t, int E, int K, float (*part)[16], float* logit) {
@@ -32,24 +32,17 @@ __device__ __forceinline__ void route_logits_by(const TX* __restrict__ x, const 
     const TX* row = x + (long long)t * K;
     for (int e0 = 0; e0 < E; e0 += R) {
         float acc[R];
+        const float* wr[R];
 #pragma unroll
-        for (int j = 0; j < R; ++j) acc[j] = 0.0f;
-        if (e0 + R <= E) {
+        for (int j = 0; j < R; ++j) {
+            acc[j] = 0.0f;
+            wr[j] = w + (long long)min(e0 + j, E - 1) * K;
+        }
 #pragma unroll 4
-            for (int k = threadIdx.x; k < K; k += 128) {
-                const float xv = to_float(row[k]);
+        for (int k = threadIdx.x; k < K; k += 128) {
+            const float xv = to_float(row[k]);
 #pragma unroll
-                for (int j = 0; j < R; ++j) acc[j] = fmaf(xv, __ldg(w + (long long)(e0 + j) * K + k), acc[j]);
-            }
-        } else {                                       // the last round of fewer than R: only its own rows are read
-            const int live = E - e0;
-#pragma unroll 4
-            for (int k = threadIdx.x; k < K; k += 128) {
-                const float xv = to_float(row[k]);
-#pragma unroll
-                for (int j = 0; j < R; ++j)
-                    if (j < live) acc[j] = fmaf(xv, __ldg(w + (long long)(e0 + j) * K + k), acc[j]);
-            }
+            for (int j = 0; j < R; ++j) acc[j] = fmaf(xv, __ldg(wr[j] + k), acc[j]);
         }
 #pragma unroll
         for (int j = 0; j < R; ++j) {
@@ -66,28 +59,31 @@ __device__ __forceinline__ void route_logits_by(const TX* __restrict__ x, const 
     }
 }
 
-// Up to eight router outputs take one round of eight; more go sixteen at a time (ten outputs: one round, not two).  An
-// output's sum is formed in the same order either way.
+// The round's size is the smallest of 4, 8, 12 and 16 that takes all outputs at once, else 16.  An output's sum is formed
+// in the same order whatever the round's size.
 template <typename TX>
 __device__ __forceinline__ void route_logits(const TX* __restrict__ x, const float* __restrict__ w, const float* __restrict__ bias,
                                              int t, int E, int K, float (*part)[16], float* logit) {
-    if (E <= 8) route_logits_by<TX, 8>(x, w, bias, t, E, K, part, logit);
+    if (E <= 4) route_logits_by<TX, 4>(x, w, bias, t, E, K, part, logit);
+    else if (E <= 8) route_logits_by<TX, 8>(x, w, bias, t, E, K, part, logit);
+    else if (E <= 12) route_logits_by<TX, 12>(x, w, bias, t, E, K, part, logit);
     else route_logits_by<TX, 16>(x, w, bias, t, E, K, part, logit);
 }
 
-template <typename TX>
+// PL: router outputs a lane of the choosing warp keeps (1 for up to 32 outputs, else 8).
+template <typename TX, int PL>
 __global__ void __launch_bounds__(128)
 moe_route_kernel(const TX* __restrict__ x, const float* __restrict__ w, const float* __restrict__ bias, int n,
                  int E, int K, int top, int* __restrict__ ids, float* __restrict__ weights) {
     const int t = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     __shared__ float part[4][16];
-    __shared__ float logit[32 * ROUTE_MAX_PER_LANE];
+    __shared__ float logit[32 * PL];
     if (w != nullptr) route_logits<TX>(x, w, bias, t, E, K, part, logit);
     if (warp != 0) return;
-    float z[ROUTE_MAX_PER_LANE];
+    float z[PL];
 #pragma unroll
-    for (int k = 0; k < ROUTE_MAX_PER_LANE; ++k) {
+    for (int k = 0; k < PL; ++k) {
         const int e = lane + 32 * k;
         z[k] = -INFINITY;
         if (e < E) z[k] = w != nullptr ? logit[e] : reinterpret_cast<const float*>(x)[(long long)t * E + e] + (bias != nullptr ? bias[e] : 0.0f);
@@ -98,7 +94,7 @@ moe_route_kernel(const TX* __restrict__ x, const float* __restrict__ w, const fl
         float best = -INFINITY;
         int where = 0x7fffffff;
 #pragma unroll
-        for (int k = 0; k < ROUTE_MAX_PER_LANE; ++k) {
+        for (int k = 0; k < PL; ++k) {
             const int e = lane + 32 * k;
             if (e < E && (z[k] > best || (z[k] == best && e < where))) {
                 best = z[k];
@@ -116,7 +112,7 @@ moe_route_kernel(const TX* __restrict__ x, const float* __restrict__ w, const fl
         }
         if (where != 0x7fffffff && (where & 31) == lane) {
 #pragma unroll
-            for (int k = 0; k < ROUTE_MAX_PER_LANE; ++k)
+            for (int k = 0; k < PL; ++k)
                 if (k == (where >> 5)) z[k] = -INFINITY;
         }
         if (lane == j) mine = best;
@@ -137,7 +133,7 @@ moe_route_kernel(const TX* __restrict__ x, const float* __restrict__ w, const fl
 // The last E - n_real outputs belong to identity experts (no matrices: the token's input itself); they are chosen and
 // weighted like the others, and whoever sums the rows treats their ids apart.  A block of four warps per token forms the
 // logits, warp 0 chooses.
-template <typename TX>
+template <typename TX, int PL>
 __global__ void __launch_bounds__(128)
 moe_route_scored_kernel(const TX* __restrict__ x, const float* __restrict__ w, const float* __restrict__ correction, int n,
                         int E, int K, int top, int G, int keep, float scale, int* __restrict__ ids,
@@ -145,15 +141,15 @@ moe_route_scored_kernel(const TX* __restrict__ x, const float* __restrict__ w, c
     const int t = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     __shared__ float part[4][16];
-    __shared__ float logit[32 * ROUTE_MAX_PER_LANE];
-    __shared__ float prob[32 * ROUTE_MAX_PER_LANE];
-    __shared__ float gscore[32 * ROUTE_MAX_PER_LANE];
+    __shared__ float logit[32 * PL];
+    __shared__ float prob[32 * PL];
+    __shared__ float gscore[32 * PL];
     route_logits<TX>(x, w, nullptr, t, E, K, part, logit);
     if (warp != 0) return;
-    float z[ROUTE_MAX_PER_LANE], c[ROUTE_MAX_PER_LANE];
+    float z[PL], c[PL];
     float m = -INFINITY;
 #pragma unroll
-    for (int k = 0; k < ROUTE_MAX_PER_LANE; ++k) {
+    for (int k = 0; k < PL; ++k) {
         const int e = lane + 32 * k;
         z[k] = e < E ? logit[e] : -INFINITY;
         m = fmaxf(m, z[k]);
@@ -161,13 +157,13 @@ moe_route_scored_kernel(const TX* __restrict__ x, const float* __restrict__ w, c
     m = warp_max(m);
     float sum = 0.0f;
 #pragma unroll
-    for (int k = 0; k < ROUTE_MAX_PER_LANE; ++k) {
+    for (int k = 0; k < PL; ++k) {
         z[k] = lane + 32 * k < E ? expf(z[k] - m) : 0.0f;
         sum += z[k];
     }
     sum = warp_sum(sum);
 #pragma unroll
-    for (int k = 0; k < ROUTE_MAX_PER_LANE; ++k) {
+    for (int k = 0; k < PL; ++k) {
         const int e = lane + 32 * k;
         z[k] = z[k] / sum;                            // the score s
         c[k] = e < E ? z[k] + (correction != nullptr ? correction[e] : 0.0f) : -INFINITY;
@@ -209,7 +205,7 @@ moe_route_scored_kernel(const TX* __restrict__ x, const float* __restrict__ w, c
             __syncwarp();
         }
 #pragma unroll
-        for (int k = 0; k < ROUTE_MAX_PER_LANE; ++k) {
+        for (int k = 0; k < PL; ++k) {
             const int e = lane + 32 * k;
             if (e < E && gscore[e / gs] != INFINITY) c[k] = -INFINITY;
         }
@@ -219,7 +215,7 @@ moe_route_scored_kernel(const TX* __restrict__ x, const float* __restrict__ w, c
         float best = -INFINITY;
         int where = 0x7fffffff;
 #pragma unroll
-        for (int k = 0; k < ROUTE_MAX_PER_LANE; ++k) {
+        for (int k = 0; k < PL; ++k) {
             const int e = lane + 32 * k;
             if (e < E && c[k] != -INFINITY && (where == 0x7fffffff || c[k] > best || (c[k] == best && e < where))) {
                 best = c[k];
@@ -237,7 +233,7 @@ moe_route_scored_kernel(const TX* __restrict__ x, const float* __restrict__ w, c
         }
         if (where != 0x7fffffff && (where & 31) == lane) {
 #pragma unroll
-            for (int k = 0; k < ROUTE_MAX_PER_LANE; ++k)
+            for (int k = 0; k < PL; ++k)
                 if (k == (where >> 5)) c[k] = -INFINITY;
         }
         if (where == 0x7fffffff) where = 0;
@@ -470,9 +466,9 @@ extern "C" int mlc_moe_route(const void* x, int x_dtype, const float* w, const f
     if (E <= 0 || E > 32 * ROUTE_MAX_PER_LANE || top <= 0 || top > 32 || top > E || (w != nullptr && K <= 0)) return MLC_ERR_BAD_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
     if (w == nullptr || x_dtype == MLC_DTYPE_F32)
-        moe_route_kernel<float><<<n, 128, 0, s>>>((const float*)x, w, bias, n, E, K, top, ids, weights);
+        (E <= 32 ? moe_route_kernel<float, 1> : moe_route_kernel<float, ROUTE_MAX_PER_LANE>)<<<n, 128, 0, s>>>((const float*)x, w, bias, n, E, K, top, ids, weights);
     else if (x_dtype == MLC_DTYPE_BF16)
-        moe_route_kernel<bf16><<<n, 128, 0, s>>>((const bf16*)x, w, bias, n, E, K, top, ids, weights);
+        (E <= 32 ? moe_route_kernel<bf16, 1> : moe_route_kernel<bf16, ROUTE_MAX_PER_LANE>)<<<n, 128, 0, s>>>((const bf16*)x, w, bias, n, E, K, top, ids, weights);
     else
         return MLC_ERR_BAD_DTYPE;
     MLC_LAUNCH_CHECK();
@@ -488,9 +484,9 @@ extern "C" int mlc_moe_route_scored(const void* x, int x_dtype, const float* w, 
     if (G > 1 && (E % G != 0 || keep < 1)) return MLC_ERR_BAD_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
     if (x_dtype == MLC_DTYPE_F32)
-        moe_route_scored_kernel<float><<<n, 128, 0, s>>>((const float*)x, w, correction, n, E, K, top, G, keep, scale, ids, weights);
+        (E <= 32 ? moe_route_scored_kernel<float, 1> : moe_route_scored_kernel<float, ROUTE_MAX_PER_LANE>)<<<n, 128, 0, s>>>((const float*)x, w, correction, n, E, K, top, G, keep, scale, ids, weights);
     else if (x_dtype == MLC_DTYPE_BF16)
-        moe_route_scored_kernel<bf16><<<n, 128, 0, s>>>((const bf16*)x, w, correction, n, E, K, top, G, keep, scale, ids, weights);
+        (E <= 32 ? moe_route_scored_kernel<bf16, 1> : moe_route_scored_kernel<bf16, ROUTE_MAX_PER_LANE>)<<<n, 128, 0, s>>>((const bf16*)x, w, correction, n, E, K, top, G, keep, scale, ids, weights);
     else
         return MLC_ERR_BAD_DTYPE;
     MLC_LAUNCH_CHECK();
