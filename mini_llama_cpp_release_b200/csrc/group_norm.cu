@@ -12,9 +12,10 @@
 //
 // Everything is float32.  A block per row: the row's v is staged in shared memory, then every group is summed by a fixed
 // set of warps (a group's warps add their parts in a fixed order), so a row's result does not depend on what else is in
-// the step.  Two forms of the same arithmetic: `group_norm_kernel<4>` moves four neighbouring entries per access (16-byte
+// the step.  Forms of the same arithmetic: `group_norm_rows_kernel` (rows of up to 4,096 entries in fours: the row stays in
+// registers, see there), `group_norm_kernel<4, .>` moves four neighbouring entries per access (16-byte
 // loads of every operand issued before any is used; rows, strides and parts that are multiples of four entries on
-// 16-byte boundaries), `group_norm_kernel<1>` takes every other size one entry at a time.
+// 16-byte boundaries), `group_norm_kernel<1, .>` takes every other size one entry at a time.
 #include "common.cuh"
 
 namespace mlc {
@@ -96,74 +97,84 @@ __device__ __forceinline__ void store_pack(const Pack<V>& r, float* xw, void* ou
     }
 }
 
-constexpr int GN_MAX_TOP = 8;        // a token's expert rows loaded side by side; more are taken in rounds of this many
+constexpr int GN_MAX_TOP = 4;        // a token's expert rows loaded side by side; more are taken in rounds of this many
 
-template <int V>
-__global__ void group_norm_kernel(GroupNormArgs a) {
+// Entries i .. i + V - 1 of row t before the norm: alpha · x + s ⊙ branch (x itself without a branch).
+// EXPERTS: the branch is the weighted sum of expert rows (a form of its own: the rows held side by side cost registers
+// that the other forms, which run far more often, then do not pay for with fewer rows in flight per SM).
+template <int V, bool EXPERTS>
+__device__ __forceinline__ Pack<V> summed_entries(const GroupNormArgs& a, const float* xr, int t, int i) {
+    const int d = a.d;
+    const bool has_branch = EXPERTS || a.y != nullptr;
+    Pack<V> val = load_pack<V>(xr, i);
+    if (has_branch) {
+        Pack<V> b, zz, zb;
+        const bool gated = a.z != nullptr;
+        if (gated) {                               // the gate's operands first: their loads overlap the branch's
+            zz = load_pack<V>(a.z, (long long)t * a.z_stride + i);
+            if (a.z_bias != nullptr) zb = load_pack<V>(a.z_bias, i);
+        }
+#pragma unroll
+        for (int k = 0; k < V; ++k) b.e[k] = 0.0f;
+        if constexpr (!EXPERTS) {
+            int s = 0;
+            for (; s + 4 <= a.slices; s += 4) {    // four slices' loads in flight, added in slice order
+                Pack<V> p[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) p[u] = load_pack<V>(a.y, ((long long)(s + u) * a.n + t) * d + i);
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+#pragma unroll
+                    for (int k = 0; k < V; ++k) b.e[k] += p[u].e[k];
+            }
+            for (; s < a.slices; ++s) {
+                const Pack<V> p = load_pack<V>(a.y, ((long long)s * a.n + t) * d + i);
+#pragma unroll
+                for (int k = 0; k < V; ++k) b.e[k] += p.e[k];
+            }
+        } else {
+            for (int j0 = 0; j0 < a.top; j0 += GN_MAX_TOP) {
+                Pack<V> p[GN_MAX_TOP];
+                float w[GN_MAX_TOP];
+#pragma unroll
+                for (int u = 0; u < GN_MAX_TOP; ++u) {
+                    const int j = j0 + u;
+                    w[u] = 0.0f;
+#pragma unroll
+                    for (int k = 0; k < V; ++k) p[u].e[k] = 0.0f;
+                    if (j < a.top) {
+                        const int r = a.row_of[(long long)t * a.top + j];
+                        w[u] = a.weights[(long long)t * a.top + j];
+                        if (r >= 0) p[u] = load_pack<V>(a.rows, (long long)r * d + i);
+                        else if (a.ident != nullptr) p[u] = load_pack_any<V>(a.ident, a.ident_dtype, (long long)t * d + i);
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < GN_MAX_TOP; ++u)
+                    if (j0 + u < a.top)
+#pragma unroll
+                        for (int k = 0; k < V; ++k) b.e[k] = fmaf(w[u], p[u].e[k], b.e[k]);
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < V; ++k) {
+            float bk = b.e[k];
+            if (gated) bk *= 1.0f / (1.0f + expf(-(zz.e[k] + (a.z_bias != nullptr ? zb.e[k] : 0.0f))));
+            val.e[k] = fmaf(a.alpha, val.e[k], bk);
+        }
+    }
+    return val;
+}
+
+template <int V, bool EXPERTS>
+__global__ void __launch_bounds__(512, 3) group_norm_kernel(GroupNormArgs a) {
     extern __shared__ __align__(16) float v[];        // [d]
     __shared__ float part[32];
     const int t = blockIdx.x;
     const int d = a.d;
     const float* xr = a.x + (long long)t * a.x_stride;
-    const bool has_branch = a.y != nullptr || a.rows != nullptr;
     for (int i = threadIdx.x * V; i < d; i += blockDim.x * V) {
-        Pack<V> val = load_pack<V>(xr, i);
-        if (has_branch) {
-            Pack<V> b, zz, zb;
-            const bool gated = a.z != nullptr;
-            if (gated) {                               // the gate's operands first: their loads overlap the branch's
-                zz = load_pack<V>(a.z, (long long)t * a.z_stride + i);
-                if (a.z_bias != nullptr) zb = load_pack<V>(a.z_bias, i);
-            }
-#pragma unroll
-            for (int k = 0; k < V; ++k) b.e[k] = 0.0f;
-            if (a.y != nullptr) {
-                int s = 0;
-                for (; s + 4 <= a.slices; s += 4) {    // four slices' loads in flight, added in slice order
-                    Pack<V> p[4];
-#pragma unroll
-                    for (int u = 0; u < 4; ++u) p[u] = load_pack<V>(a.y, ((long long)(s + u) * a.n + t) * d + i);
-#pragma unroll
-                    for (int u = 0; u < 4; ++u)
-#pragma unroll
-                        for (int k = 0; k < V; ++k) b.e[k] += p[u].e[k];
-                }
-                for (; s < a.slices; ++s) {
-                    const Pack<V> p = load_pack<V>(a.y, ((long long)s * a.n + t) * d + i);
-#pragma unroll
-                    for (int k = 0; k < V; ++k) b.e[k] += p.e[k];
-                }
-            } else {
-                for (int j0 = 0; j0 < a.top; j0 += GN_MAX_TOP) {
-                    Pack<V> p[GN_MAX_TOP];
-                    float w[GN_MAX_TOP];
-#pragma unroll
-                    for (int u = 0; u < GN_MAX_TOP; ++u) {
-                        const int j = j0 + u;
-                        w[u] = 0.0f;
-#pragma unroll
-                        for (int k = 0; k < V; ++k) p[u].e[k] = 0.0f;
-                        if (j < a.top) {
-                            const int r = a.row_of[(long long)t * a.top + j];
-                            w[u] = a.weights[(long long)t * a.top + j];
-                            if (r >= 0) p[u] = load_pack<V>(a.rows, (long long)r * d + i);
-                            else if (a.ident != nullptr) p[u] = load_pack_any<V>(a.ident, a.ident_dtype, (long long)t * d + i);
-                        }
-                    }
-#pragma unroll
-                    for (int u = 0; u < GN_MAX_TOP; ++u)
-                        if (j0 + u < a.top)
-#pragma unroll
-                            for (int k = 0; k < V; ++k) b.e[k] = fmaf(w[u], p[u].e[k], b.e[k]);
-                }
-            }
-#pragma unroll
-            for (int k = 0; k < V; ++k) {
-                float bk = b.e[k];
-                if (gated) bk *= 1.0f / (1.0f + expf(-(zz.e[k] + (a.z_bias != nullptr ? zb.e[k] : 0.0f))));
-                val.e[k] = fmaf(a.alpha, val.e[k], bk);
-            }
-        }
+        const Pack<V> val = summed_entries<V, EXPERTS>(a, xr, t, i);
 #pragma unroll
         for (int k = 0; k < V; ++k) v[i + k] = val.e[k];
     }
@@ -207,6 +218,54 @@ __global__ void group_norm_kernel(GroupNormArgs a) {
     }
 }
 
+// The same norm with the row held in registers: thread th keeps the NP packs of four entries th, th + threads, ... of
+// the row, so the row is read once and nothing but one sum of squares per pack goes through shared memory.  Warp w sums
+// the packs of groups w, w + warps, ... (a lane a strided share in order, then the warp's tree), so a group's statistic is
+// formed in an order that only the row's length and the number of groups fix.  Rows of up to 4 · NP · 512 entries.
+template <int NP, bool EXPERTS>
+__global__ void __launch_bounds__(512, 3) group_norm_rows_kernel(GroupNormArgs a) {
+    extern __shared__ __align__(16) float v[];        // [d / 4] sums of squares of the packs, then [groups] factors
+    const int t = blockIdx.x;
+    const int d = a.d, packs = d >> 2;
+    const float* xr = a.x + (long long)t * a.x_stride;
+    Pack<4> val[NP];
+#pragma unroll
+    for (int u = 0; u < NP; ++u) {
+        const int p = threadIdx.x + u * blockDim.x;
+        if (p < packs) {
+            val[u] = summed_entries<4, EXPERTS>(a, xr, t, p << 2);
+            float ss = 0.0f;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) ss = fmaf(val[u].e[k], val[u].e[k], ss);
+            v[p] = ss;
+        }
+    }
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+    const int gsize = d / a.groups, ppg = gsize >> 2;
+    float* factor = v + packs;
+    for (int g = warp; g < a.groups; g += n_warps) {
+        float ss = 0.0f;
+        for (int j = lane; j < ppg; j += 32) ss += v[g * ppg + j];
+        ss = warp_sum(ss);
+        if (lane == 0) factor[g] = 1.0f / sqrtf(ss / (float)gsize + a.eps);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int u = 0; u < NP; ++u) {
+        const int p = threadIdx.x + u * blockDim.x;
+        if (p < packs) {
+            const int i = p << 2;
+            const float f = factor[i / gsize];
+            const Pack<4> gn = load_pack<4>(a.gain, i % a.gain_len);
+            Pack<4> r;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) r.e[k] = val[u].e[k] * f * gn.e[k];
+            store_pack<4>(r, a.write_x ? a.x : nullptr, a.out, a.out_dtype, (long long)t * a.x_stride + i, (long long)t * d + i);
+        }
+    }
+}
+
 // out = act(in), elementwise: 0 silu, 1 gelu (erf), 2 gelu with the tanh approximation.  float32 arithmetic.
 template <typename TI, typename TO>
 __global__ void activation_kernel(const TI* __restrict__ in, long long total, int kind, TO* __restrict__ out) {
@@ -241,13 +300,22 @@ extern "C" int mlc_group_norm(float* x, long long x_stride, int n, int d, int gr
     const bool by_four = gsize % 4 == 0 && gain_len % 4 == 0 && x_stride % 4 == 0 && (z == nullptr || z_stride % 4 == 0) &&
                          aligned(x) && aligned(gain) && aligned(y) && aligned(rows) && aligned(ident) && aligned(z) &&
                          aligned(z_bias) && aligned(out);
-    if (by_four) {
+    if (by_four && d <= 4096) {
+        // the row in registers: one pack of four entries a thread up to 512 threads, two beyond
+        const int packs = d / 4, np = packs <= 512 ? 1 : 2;
+        int threads = (((packs + np - 1) / np + 31) / 32) * 32;
+        threads = threads < 32 ? 32 : threads;
+        const size_t shared = (size_t)(packs + groups) * sizeof(float);
+        auto kernel = rows != nullptr ? (np == 1 ? group_norm_rows_kernel<1, true> : group_norm_rows_kernel<2, true>)
+                                      : (np == 1 ? group_norm_rows_kernel<1, false> : group_norm_rows_kernel<2, false>);
+        kernel<<<n, threads, shared, (cudaStream_t)stream>>>(a);
+    } else if (by_four) {
         int threads = ((d / 4 + 31) / 32) * 32;        // a thread per four entries, up to 512 threads a row
         threads = threads < 64 ? 64 : (threads > 512 ? 512 : threads);
-        group_norm_kernel<4><<<n, threads, (size_t)d * sizeof(float), (cudaStream_t)stream>>>(a);
+        (rows != nullptr ? group_norm_kernel<4, true> : group_norm_kernel<4, false>)<<<n, threads, (size_t)d * sizeof(float), (cudaStream_t)stream>>>(a);
     } else {
         const int threads = d <= 256 ? 64 : (d <= 1024 ? 128 : 256);
-        group_norm_kernel<1><<<n, threads, (size_t)d * sizeof(float), (cudaStream_t)stream>>>(a);
+        (rows != nullptr ? group_norm_kernel<1, true> : group_norm_kernel<1, false>)<<<n, threads, (size_t)d * sizeof(float), (cudaStream_t)stream>>>(a);
     }
     MLC_LAUNCH_CHECK();
     return 0;
