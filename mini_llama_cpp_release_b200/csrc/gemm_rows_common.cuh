@@ -36,10 +36,27 @@ struct RowsArgs {
     int act;
 };
 
-__device__ __forceinline__ float rows_activation(float z, int act) {
-    if (act == 1) return z / (1.0f + expf(-z));
-    if (act == 2) return 0.5f * z * (1.0f + erff(z * 0.70710678118654752440f));
-    return 0.5f * z * (1.0f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
+// One activation over a chunk of accumulator columns.  The kind is tested once per chunk, outside the unrolled loop: with
+// the test inside, the loop's body holds all three functions, is not unrolled, and the chunk is indexed through local
+// memory (a product with an activation then took 1.7 times the time of the same product without one).
+template <int ACT>
+__device__ __forceinline__ float rows_activation(float z) {
+    if constexpr (ACT == 1) return z / (1.0f + expf(-z));
+    else if constexpr (ACT == 2) return 0.5f * z * (1.0f + erff(z * 0.70710678118654752440f));
+    else return 0.5f * z * (1.0f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
+}
+
+__device__ __forceinline__ void rows_activate(float (&v)[32], int act) {
+    if (act == 1) {
+#pragma unroll
+        for (int u = 0; u < 32; ++u) v[u] = rows_activation<1>(v[u]);
+    } else if (act == 2) {
+#pragma unroll
+        for (int u = 0; u < 32; ++u) v[u] = rows_activation<2>(v[u]);
+    } else {
+#pragma unroll
+        for (int u = 0; u < 32; ++u) v[u] = rows_activation<3>(v[u]);
+    }
 }
 
 constexpr int R_BM = 128;
@@ -60,10 +77,7 @@ __device__ __forceinline__ void rows_epilogue_chunk(const RowsArgs& g, const flo
     float v[32];
 #pragma unroll
     for (int u = 0; u < 32; ++u) v[u] = vin[u];
-    if (EPI == R_EPI_STORE && g.act != 0) {
-#pragma unroll
-        for (int u = 0; u < 32; ++u) v[u] = rows_activation(v[u], g.act);
-    }
+    if (EPI == R_EPI_STORE && g.act != 0) rows_activate(v, g.act);
     if (EPI == R_EPI_STORE) {
         if (g.out_dtype == MLC_DTYPE_BF16) {
             uint4* dst = reinterpret_cast<uint4*>((bf16*)g.out + (long long)tok * g.n_out + n);
