@@ -71,6 +71,11 @@ def plan_groups(needs: Sequence[Optional[CacheNeed]], reads_cache_of: Sequence[O
                 raise ValueError(f"schedule entry {e} cannot read the cache of entry {src}: it reads "
                                  f"{'all keys' if needs[e].kind != 'window' else f'a window of {needs[e].window}'}, "
                                  f"the owner keeps a window of {needs[src].window}")
+            if needs[e] is not None and needs[src] is not None and needs[src].kind == "chunk" and (
+                    needs[e].kind != "chunk" or needs[e].window != needs[src].window):
+                # the owner gives a chunk's pages back once the sequence has left the chunk
+                raise ValueError(f"schedule entry {e} cannot read the cache of entry {src}: the owner keeps chunks of "
+                                 f"{needs[src].window} keys, and the reader's mask is not the same")
             where[e] = where[src]
     return groups, where
 
@@ -173,8 +178,9 @@ class SlotBook:
         L = self.length[slot]
         for g, layout in enumerate(self.groups):
             w = layout.need.window
-            if layout.need.kind == "window" and w:
-                first_needed = max(0, L - w + 1)                 # the next token reads keys from here on
+            if layout.need.kind in ("window", "chunk") and w:
+                # the next token reads keys from here on: the window's first key, or the first key of the chunk it falls into
+                first_needed = max(0, L - w + 1) if layout.need.kind == "window" else (L // w) * w
                 plist = self.page_lists[slot][g]
                 kept = (layout.need.keep_first + self.page_size - 1) // self.page_size   # pages of first keys that stay visible
                 for i in range(kept, min(len(plist), first_needed // self.page_size)):

@@ -7,7 +7,9 @@
 // each sequence q_len new tokens at positions start_pos .. start_pos + q_len - 1, their
 // keys and values are already in the cache, and a token at position p reads keys
 // lo(p) .. p, with lo(p) = 0 or p - window + 1, and beside a window the first `keep_first`
-// keys of the sequence, which stay visible at any distance (at their true positions).  The reference computes the same thing
+// keys of the sequence, which stay visible at any distance (at their true positions).  With `chunk` the mask is one of
+// chunks instead: lo(p) = (p / chunk) * chunk, counted from the sequence's first position.  With `softcap` a score
+// becomes softcap * tanh(score / softcap) before the softmax.  The reference computes the same thing
 // one (head, position) at a time: score = (q·k)·1/sqrt(hd), max, exp, sum, weighted sum
 // of values (src/forward.cpp:585-611; src/ops.cpp:43-70); query head h reads kv head
 // h / (H/KV) (src/forward.cpp:524-526).  Here a block holds up to 16 (token, head) rows
@@ -37,6 +39,8 @@ struct AttnArgs {
     int group;                // query heads per kv head
     int window;               // 0: all keys
     int keep_first;           // with a window: keys at positions below this stay visible whatever the distance
+    int chunk;                // > 0: a token at position p reads only the keys from (p / chunk) * chunk on (a mask of chunks)
+    float softcap;            // > 0: score <- softcap * tanh(score / softcap), after the scale
     int tokens_per_block;     // TQ
     int heads_per_block;      // GH, TQ*GH <= 16
     int head_chunks;          // ceil(group / GH)
@@ -82,7 +86,7 @@ attention_simt_kernel(AttnArgs a, PagedKV c) {
 
     // key range of the block and of this split
     const int p_first = start + tok0, p_last = start + tok0 + n_tok - 1;
-    const int lo_block = (a.window > 0) ? max(0, p_first - a.window + 1) : 0;
+    const int lo_block = (a.chunk > 0) ? (p_first / a.chunk) * a.chunk : (a.window > 0) ? max(0, p_first - a.window + 1) : 0;
     const int tile_begin = lo_block / ATT_TILE, tile_end = p_last / ATT_TILE + 1;
     // tiles of kept first keys that lie before the window's first tile are walked ahead of it: the walk's tile number
     // v stands for tile v below `head_tiles`, and for tile_begin + (v - head_tiles) from there on
@@ -102,7 +106,7 @@ attention_simt_kernel(AttnArgs a, PagedKV c) {
         const int t = r / a.heads_per_block, hg = chunk * a.heads_per_block + r % a.heads_per_block;
         row_ok[i] = (t < n_tok) && (hg < a.group);
         row_hi[i] = start + tok0 + t;
-        row_lo[i] = (a.window > 0) ? max(0, row_hi[i] - a.window + 1) : 0;
+        row_lo[i] = (a.chunk > 0) ? (row_hi[i] / a.chunk) * a.chunk : (a.window > 0) ? max(0, row_hi[i] - a.window + 1) : 0;
         m[i] = -INFINITY;
         l[i] = 0.0f;
 #pragma unroll
@@ -144,6 +148,7 @@ attention_simt_kernel(AttnArgs a, PagedKV c) {
                 float dot = 0.0f;
                 for (int d = 0; d < hd; ++d) dot += qr[d] * kr[d];
                 s = dot * a.scale;
+                if (a.softcap > 0.0f) s = a.softcap * tanhf(s / a.softcap);
             }
             const float tile_max = warp_max(s);
             if (tile_max == -INFINITY) continue;
@@ -245,11 +250,13 @@ static int launch_attention_simt(const void* q, void* out, int dtype, const int*
                                  int n_seqs, int n_tokens, int max_q_len, int q_heads, int kv_heads, int hd, float scale,
                                  int window, int n_splits, float* part_ml, float* part_o, void* k_pool, void* v_pool,
                                  const int* page_table, long long entry_offset, int pages_per_seq, int page_size,
-                                 cudaStream_t s, const float* sinks = nullptr, int keep_first = 0) {
+                                 cudaStream_t s, const float* sinks = nullptr, int keep_first = 0, int chunk = 0,
+                                 float softcap = 0.0f) {
     if (n_seqs <= 0 || n_tokens <= 0) return 0;
     if (hd <= 0 || hd > ATT_MAX_HD || q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads != 0) return MLC_ERR_BAD_SIZE;
     if (n_splits < 1 || (n_splits > 1 && (part_ml == nullptr || part_o == nullptr))) return MLC_ERR_BAD_SIZE;
     if (n_seqs > 65535) return MLC_ERR_BAD_SIZE;
+    if (chunk < 0 || (chunk > 0 && window > 0) || softcap < 0.0f) return MLC_ERR_UNSUPPORTED;
     if (dtype != MLC_DTYPE_F32 && dtype != MLC_DTYPE_BF16) return MLC_ERR_BAD_DTYPE;
     AttnArgs a;
     a.q = q;
@@ -264,6 +271,8 @@ static int launch_attention_simt(const void* q, void* out, int dtype, const int*
     a.group = q_heads / kv_heads;
     a.window = window;
     a.keep_first = keep_first < 0 ? 0 : keep_first;
+    a.chunk = chunk;
+    a.softcap = softcap;
     a.heads_per_block = a.group < ATT_ROWS ? a.group : ATT_ROWS;
     a.tokens_per_block = ATT_ROWS / a.heads_per_block;
     a.head_chunks = (a.group + a.heads_per_block - 1) / a.heads_per_block;
@@ -321,10 +330,10 @@ extern "C" int mlc_attention_simt(const void* q, void* out, int dtype, const int
                                   int kv_heads, int hd, float scale, int window, int n_splits, float* part_ml,
                                   float* part_o, void* k_pool, void* v_pool, const int* page_table,
                                   long long entry_offset, int pages_per_seq, int page_size, const float* sinks, int keep_first,
-                                  void* stream) {
+                                  int chunk, float softcap, void* stream) {
     return launch_attention_simt(q, out, dtype, cu_seqlens, start_pos, n_seqs, n_tokens, max_q_len, q_heads, kv_heads, hd,
                                  scale, window, n_splits, part_ml, part_o, k_pool, v_pool, page_table, entry_offset,
-                                 pages_per_seq, page_size, (cudaStream_t)stream, sinks, keep_first);
+                                 pages_per_seq, page_size, (cudaStream_t)stream, sinks, keep_first, chunk, softcap);
 }
 
 // Merge partial results that another attention kernel left in part_ml / part_o

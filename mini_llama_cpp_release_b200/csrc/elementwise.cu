@@ -454,13 +454,25 @@ static cudaError_t launch_layernorm_warp(int nv, float* x, const float* y, int n
 // applied); the rest pass.  v is multiplied by v_scale.  q goes to q_out [token][head][D], k and v into the token's
 // place in the cache, whose heads have D >= max(dim, vdim) entries: what lies beyond a head's own size is zero, which
 // changes neither a score nor an output.  A warp per head.
+// Options of the kernel below beyond its first form: biases added to the projection's columns as they are read (null:
+// none); `whole_row`: the norm's statistic is taken over all query heads together (and over all key heads together) and the
+// gains are as long as the projection, instead of one statistic per head and a gain shared by the heads; `interleaved`: the
+// rotation pairs entry 2j with 2j + 1 instead of entry j with j + dims/2.
+struct QkOptions {
+    const float* q_bias;
+    const float* k_bias;
+    const float* v_bias;
+    int whole_row;
+    int interleaved;
+};
+
 template <typename T>
 __global__ void qk_norm_rope_cache_kernel(const float* __restrict__ proj, long long stride, int q_col, int k_col, int v_col,
                                           const float* __restrict__ q_gain, const float* __restrict__ k_gain, float eps,
                                           const int* __restrict__ positions, const int* __restrict__ tok_seq,
                                           const float2* __restrict__ rope, int rope_positions, int rot_dims, int q_heads,
                                           int kv_heads_in_row, int dim, int vdim, int D, float v_scale, T* __restrict__ q_out,
-                                          PagedKV cache) {
+                                          PagedKV cache, QkOptions opt) {
     const int n = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
     const float* row = proj + (long long)n * stride;
@@ -469,27 +481,62 @@ __global__ void qk_norm_rope_cache_kernel(const float* __restrict__ proj, long l
     const int half = rot_dims >> 1;
     const float2* cs = (rope != nullptr && half > 0) ? rope + (long long)min(p, rope_positions - 1) * half : nullptr;
     const int n_heads = q_heads + 2 * kv_heads_in_row;
+    // a norm over the whole projection: one statistic for all query heads and one for all key heads, summed in an order
+    // that the row's length alone fixes (a thread a strided share, then the block's tree)
+    __shared__ float scratch[32];
+    float f_q = 1.0f, f_k = 1.0f;
+    if (opt.whole_row && eps >= 0.0f) {
+        float ss = 0.0f;
+        for (int i = threadIdx.x; i < q_heads * dim; i += blockDim.x) {
+            const float v = row[q_col + i] + (opt.q_bias != nullptr ? opt.q_bias[i] : 0.0f);
+            ss += v * v;
+        }
+        f_q = 1.0f / sqrtf(block_sum(ss, scratch) / (float)(q_heads * dim) + eps);
+        if (kv_heads_in_row > 0) {
+            ss = 0.0f;
+            for (int i = threadIdx.x; i < kv_heads_in_row * dim; i += blockDim.x) {
+                const float v = row[k_col + i] + (opt.k_bias != nullptr ? opt.k_bias[i] : 0.0f);
+                ss += v * v;
+            }
+            f_k = 1.0f / sqrtf(block_sum(ss, scratch) / (float)(kv_heads_in_row * dim) + eps);
+        }
+    }
     for (int head = warp; head < n_heads; head += n_warps) {
         if (head < q_heads + kv_heads_in_row) {
             const bool is_q = head < q_heads;
-            const float* src = row + (is_q ? q_col + head * dim : k_col + (head - q_heads) * dim);
+            const int h = is_q ? head : head - q_heads;
+            const float* src = row + (is_q ? q_col : k_col) + h * dim;
+            const float* bias = is_q ? opt.q_bias : opt.k_bias;
+            if (bias != nullptr) bias += h * dim;
             const float* gain = is_q ? q_gain : k_gain;
+            if (gain != nullptr && opt.whole_row) gain += h * dim;             // a gain as long as the projection
             T* dst = is_q ? q_out + ((long long)n * q_heads + head) * D
-                          : (T*)cache.k_pool + paged_offset(cache, seq, p, head - q_heads);
-            float ss = 0.0f;
-            for (int i = lane; i < dim; i += 32) ss += src[i] * src[i];
-            ss = warp_sum(ss);
-            const float f = eps >= 0.0f ? 1.0f / sqrtf(ss / (float)dim + eps) : 1.0f;      // a negative eps: no norm
+                          : (T*)cache.k_pool + paged_offset(cache, seq, p, h);
+            float f = is_q ? f_q : f_k;
+            if (!opt.whole_row) {
+                float ss = 0.0f;
+                for (int i = lane; i < dim; i += 32) {
+                    const float v = src[i] + (bias != nullptr ? bias[i] : 0.0f);
+                    ss += v * v;
+                }
+                ss = warp_sum(ss);
+                f = eps >= 0.0f ? 1.0f / sqrtf(ss / (float)dim + eps) : 1.0f;      // a negative eps: no norm
+            }
             for (int i = lane; i < D; i += 32) {
                 float v = 0.0f;
                 if (i < dim) {
-                    v = gain != nullptr ? src[i] * f * gain[i] : src[i] * f;
+                    const float raw = src[i] + (bias != nullptr ? bias[i] : 0.0f);
+                    v = gain != nullptr ? raw * f * gain[i] : raw * f;
                     if (cs != nullptr && i < rot_dims) {
-                        const int j = i < half ? i : i - half;
-                        const int partner = i < half ? i + half : i - half;
-                        const float w = gain != nullptr ? src[partner] * f * gain[partner] : src[partner] * f;
+                        // the pair of entry i: i +- dims/2 (halves), or its neighbour 2j, 2j+1 (interleaved); the first of a
+                        // pair becomes u cos - w sin, the second w cos + u sin
+                        const bool first = opt.interleaved ? (i & 1) == 0 : i < half;
+                        const int j = opt.interleaved ? i >> 1 : (i < half ? i : i - half);
+                        const int partner = opt.interleaved ? (i ^ 1) : (i < half ? i + half : i - half);
+                        const float praw = src[partner] + (bias != nullptr ? bias[partner] : 0.0f);
+                        const float w = gain != nullptr ? praw * f * gain[partner] : praw * f;
                         const float2 t = cs[j];
-                        v = i < half ? v * t.x - w * t.y : v * t.x + w * t.y;
+                        v = first ? v * t.x - w * t.y : v * t.x + w * t.y;
                     }
                 }
                 dst[i] = from_float<T>(v);
@@ -497,8 +544,10 @@ __global__ void qk_norm_rope_cache_kernel(const float* __restrict__ proj, long l
         } else {
             const int vh = head - q_heads - kv_heads_in_row;
             const float* src = row + v_col + vh * vdim;
+            const float* bias = opt.v_bias != nullptr ? opt.v_bias + vh * vdim : nullptr;
             T* dst = (T*)cache.v_pool + paged_offset(cache, seq, p, vh);
-            for (int i = lane; i < D; i += 32) dst[i] = from_float<T>(i < vdim ? src[i] * v_scale : 0.0f);
+            for (int i = lane; i < D; i += 32)
+                dst[i] = from_float<T>(i < vdim ? (src[i] + (bias != nullptr ? bias[i] : 0.0f)) * v_scale : 0.0f);
         }
     }
 }
@@ -612,8 +661,10 @@ extern "C" int mlc_qk_norm_rope_cache(const float* proj, long long stride, int q
                                       const void* rope_table, int rope_positions, int rot_dims, int n, int q_heads,
                                       int kv_heads_in_row, int dim, int vdim, int D, float v_scale, void* q_out, int dtype,
                                       void* k_pool, void* v_pool, const int* page_table, long long entry_offset,
-                                      int pages_per_seq, int page_size, int cache_kv_heads, void* stream) {
+                                      int pages_per_seq, int page_size, int cache_kv_heads, const float* q_bias,
+                                      const float* k_bias, const float* v_bias, int whole_row, int interleaved, void* stream) {
     if (n <= 0) return 0;
+    const QkOptions opt{q_bias, k_bias, v_bias, whole_row, interleaved};
     if (dim <= 0 || vdim <= 0 || D < dim || D < vdim || q_heads <= 0 || kv_heads_in_row < 0) return MLC_ERR_BAD_SIZE;
     if (rot_dims < 0 || (rot_dims & 1) || rot_dims > dim) return MLC_ERR_BAD_SIZE;
     if (kv_heads_in_row != 0 && kv_heads_in_row != cache_kv_heads) return MLC_ERR_BAD_SIZE;
@@ -624,11 +675,11 @@ extern "C" int mlc_qk_norm_rope_cache(const float* proj, long long stride, int q
     if (dtype == MLC_DTYPE_F32)
         qk_norm_rope_cache_kernel<float><<<n, threads, 0, s>>>(proj, stride, q_col, k_col, v_col, q_gain, k_gain, eps, positions,
                                                                tok_seq, (const float2*)rope_table, rope_positions, rot_dims, q_heads,
-                                                               kv_heads_in_row, dim, vdim, D, v_scale, (float*)q_out, c);
+                                                               kv_heads_in_row, dim, vdim, D, v_scale, (float*)q_out, c, opt);
     else if (dtype == MLC_DTYPE_BF16)
         qk_norm_rope_cache_kernel<bf16><<<n, threads, 0, s>>>(proj, stride, q_col, k_col, v_col, q_gain, k_gain, eps, positions,
                                                               tok_seq, (const float2*)rope_table, rope_positions, rot_dims, q_heads,
-                                                              kv_heads_in_row, dim, vdim, D, v_scale, (bf16*)q_out, c);
+                                                              kv_heads_in_row, dim, vdim, D, v_scale, (bf16*)q_out, c, opt);
     else
         return MLC_ERR_BAD_DTYPE;
     MLC_LAUNCH_CHECK();

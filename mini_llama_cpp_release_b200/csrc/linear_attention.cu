@@ -42,6 +42,12 @@ struct GlaArgs {
     long long out_slice;        // floats between the slices of two row slabs
     int H, dim, vdim;
     int col_slabs;
+    // a state-space layer's use of the walk: `qk_share` heads in a row read the same q and k (head h reads group h / qk_share;
+    // 1: every head its own), `head_decay` [n][H] is one decay per token and head for all of a head's rows (then `decay` is
+    // not read), `v_scale` [n][H] multiplies the head's v as it is read.  Null: the ordinary forms.
+    int qk_share;
+    const float* head_decay;
+    const float* v_scale;
 };
 
 // z <- sigmoid(z + bias)^(1/tau) = exp(logsigmoid(z + bias) / tau),  logsigmoid(x) = min(x, 0) - log1p(exp(-|x|))
@@ -129,10 +135,11 @@ gla_walk_kernel(GlaArgs a) {
             rq[u] = rk[u] = 0.0f;
             ra[u] = 1.0f;                             // no token, or no such channel: a decay of one, q and k zero
             if (tt < n_here && row0 + d < dim) {
-                const float* row = a.qk + (long long)(c0 + tt) * a.qk_stride + head * dim + row0 + d;
+                const float* row = a.qk + (long long)(c0 + tt) * a.qk_stride + (head / a.qk_share) * dim + row0 + d;
                 rq[u] = row[a.q_col];
                 rk[u] = row[a.k_col];
-                ra[u] = a.decay[(long long)(c0 + tt) * a.H * dim + head * dim + row0 + d];
+                ra[u] = a.head_decay != nullptr ? a.head_decay[(long long)(c0 + tt) * a.H + head]
+                                                : a.decay[(long long)(c0 + tt) * a.H * dim + head * dim + row0 + d];
             }
         }
 #pragma unroll
@@ -140,6 +147,7 @@ gla_walk_kernel(GlaArgs a) {
             const int idx = tid + u * GLA_THREADS;
             const int tt = idx / GLA_COLS, cc = idx % GLA_COLS;
             rv[u] = (tt < n_here && col0 + cc < vdim) ? a.vsrc[(long long)(c0 + tt) * a.v_stride + a.v_col + head * vdim + col0 + cc] : 0.0f;
+            if (a.v_scale != nullptr && tt < n_here) rv[u] *= a.v_scale[(long long)(c0 + tt) * a.H + head];
         }
     };
     if (t0 < t1) fetch(t0);
@@ -208,6 +216,58 @@ gla_walk_kernel(GlaArgs a) {
         }
 }
 
+
+// The state-space layer ("Mamba-2"; Dao and Gu, "Transformers are SSMs: Generalized Models and Efficient Algorithms Through
+// Structured State Space Duality"): per head a state S [N][vdim] with one decay per token and head,
+//   dt = softplus(z_dt + bias),   S_t = exp(-exp(A_log) · dt) S_{t-1} + dt · B_t x_tᵀ,   y_t = S_tᵀ C_t + D x_t
+// which is the walk above with decay exp(-exp(A_log) dt) for all rows of a head, key B and query C of the head's group, value
+// dt · x.  This kernel makes dt and the decay per (token, head), float32, with no clamp:
+// softplus(v) = max(v, 0) + log1p(exp(-|v|)).
+__global__ void state_space_steps_kernel(const float* __restrict__ proj, long long stride, int dt_col, const float* __restrict__ dt_bias,
+                                         const float* __restrict__ A_log, long long total, int H, float* __restrict__ dt_out,
+                                         float* __restrict__ decay_out) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const long long t = idx / H;
+    const int h = (int)(idx - t * H);
+    const float v = proj[t * stride + dt_col + h] + dt_bias[h];
+    const float dt = fmaxf(v, 0.0f) + log1pf(expf(-fabsf(v)));
+    dt_out[idx] = dt;
+    decay_out[idx] = expf(-expf(A_log[h]) * dt);
+}
+
+// Behind the walk: y = (sum of the walk's slices + D_h · x) · silu(z); the row in `groups` equal parts, each divided by its own
+// sqrt(mean(part²) + eps); times the gain; in the engine's type.  A block per token forms y into shared memory; then a warp takes parts in turn (a
+// lane a strided share of the part, then the warp's tree: an order fixed by the sizes alone).
+template <typename T>
+__global__ void state_space_finish_kernel(const float* __restrict__ o, int slices, long long slice_stride,
+                                          const float* __restrict__ xsrc, long long x_stride, const float* __restrict__ D,
+                                          const float* __restrict__ z, long long z_stride, const float* __restrict__ gain, float eps,
+                                          int H, int vdim, int groups, T* __restrict__ out) {
+    const long long t = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+    const int inner = H * vdim, part = inner / groups;
+    extern __shared__ float row[];                       // [inner]
+    for (int c = threadIdx.x; c < inner; c += blockDim.x) {
+        float y = 0.0f;
+        for (int s = 0; s < slices; ++s) y += o[(long long)s * slice_stride + t * inner + c];
+        y = fmaf(D[c / vdim], xsrc[t * x_stride + c], y);
+        const float zz = z[t * z_stride + c];
+        row[c] = y * (zz / (1.0f + expf(-zz)));
+    }
+    __syncthreads();
+    for (int g = warp; g < groups; g += n_warps) {
+        float ss = 0.0f;
+        for (int i = lane; i < part; i += 32) ss += row[g * part + i] * row[g * part + i];
+        ss = warp_sum(ss);
+        const float f = 1.0f / sqrtf(ss / (float)part + eps);
+        for (int i = lane; i < part; i += 32) {
+            const int c = g * part + i;
+            out[t * inner + c] = from_float<T>(row[c] * f * gain[c]);
+        }
+    }
+}
+
 template <int ROWS>
 static int launch_gla(const GlaArgs& a, dim3 grid, cudaStream_t s) {
     constexpr int DP = 8 * ROWS;
@@ -243,12 +303,12 @@ extern "C" int mlc_gla_rows(int n_seqs, int H, int dim, int vdim, int n_sms) {
 static int gla_walk(const float* qk, long long qk_stride, int q_col, int k_col, const float* v, long long v_stride, int v_col,
                     const float* decay, float q_scale, float* state, long long state_stride, const int* slots,
                     const int* cu_seqlens, int n_seqs, int n_tokens, int H, int dim, int vdim, int rows, float* out,
-                    cudaStream_t s) {
-    if (H <= 0 || dim <= 0 || dim > 256 || vdim <= 0 || n_seqs > 65535) return MLC_ERR_BAD_SIZE;
+                    cudaStream_t s, int qk_share = 1, const float* head_decay = nullptr, const float* v_scale = nullptr) {
+    if (H <= 0 || dim <= 0 || dim > 256 || vdim <= 0 || n_seqs > 65535 || qk_share < 1 || H % qk_share) return MLC_ERR_BAD_SIZE;
     if (rows != 2 && rows != 4 && rows != 8 && rows != 16 && rows != 32) return MLC_ERR_BAD_SIZE;
     const int col_slabs = (vdim + GLA_COLS - 1) / GLA_COLS, row_slabs = (dim + 8 * rows - 1) / (8 * rows);
     GlaArgs a{qk, qk_stride, v, v_stride, q_col, k_col, v_col, decay, q_scale, state, state_stride,
-              slots, cu_seqlens, out, (long long)n_tokens * H * vdim, H, dim, vdim, col_slabs};
+              slots, cu_seqlens, out, (long long)n_tokens * H * vdim, H, dim, vdim, col_slabs, qk_share, head_decay, v_scale};
     const dim3 grid(H, n_seqs, col_slabs * row_slabs);
     if (rows == 2) return launch_gla<2>(a, grid, s);
     if (rows == 4) return launch_gla<4>(a, grid, s);
@@ -293,4 +353,39 @@ extern "C" int mlc_forget_gate_attention(const float* proj, long long proj_strid
     MLC_LAUNCH_CHECK();
     return gla_walk(qk, 2LL * width, 0, width, proj, proj_stride, v_col, decay, 1.0f, state, state_stride, slots, cu_seqlens,
                     n_seqs, n_tokens, H, dim, vdim, rows, out, s);
+}
+
+// The state-space layer.  proj: float32 rows holding the gate z (H x vdim) at z_col and the step logits (H) at dt_col; xbc:
+// float32 rows (what the convolution and its activation left) holding x (H x vdim) at column 0, B (G x N) at b_col and C
+// (G x N) at c_col; head h reads group h / (H / G).  dt, decay: float32 [n][H] scratch that this call fills.  state: float32, a
+// slot's row holds H*vdim*N floats ([head][column][row]).  rows: what mlc_gla_rows gave for (n_seqs, H, N, vdim).  walk: float32
+// [ceil(N / (8 * rows))][n][H*vdim] scratch (the walk's partial outputs).  out [n][H*vdim] of out_dtype: the gated, normed y.
+extern "C" int mlc_state_space(const float* proj, long long proj_stride, int z_col, int dt_col, const float* xbc, long long xbc_stride,
+                               int b_col, int c_col, const float* dt_bias, const float* A_log, const float* D, const float* gain,
+                               float eps, int norm_groups, float* dt, float* decay, float* state, long long state_stride,
+                               const int* slots, const int* cu_seqlens, int n_seqs, int n_tokens, int H, int G, int N, int vdim,
+                               int rows, float* walk, void* out, int out_dtype, void* stream) {
+    if (n_seqs <= 0 || n_tokens <= 0) return 0;
+    if (H <= 0 || G <= 0 || H % G || N <= 0 || N > 256 || vdim <= 0 || n_seqs > 65535) return MLC_ERR_BAD_SIZE;
+    const int inner = H * vdim;
+    if (norm_groups < 1 || inner % norm_groups || inner * sizeof(float) > 48 * 1024) return MLC_ERR_BAD_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+    const long long total = (long long)n_tokens * H;
+    state_space_steps_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(proj, proj_stride, dt_col, dt_bias, A_log, total, H, dt, decay);
+    MLC_LAUNCH_CHECK();
+    const int rc = gla_walk(xbc, xbc_stride, c_col, b_col, xbc, xbc_stride, 0, nullptr, 1.0f, state, state_stride, slots, cu_seqlens,
+                            n_seqs, n_tokens, H, N, vdim, rows, walk, s, H / G, decay, dt);
+    if (rc != 0) return rc;
+    const int slices = (N + 8 * rows - 1) / (8 * rows);
+    const int warps = inner >= 1024 ? 8 : 4;
+    if (out_dtype == MLC_DTYPE_F32)
+        state_space_finish_kernel<float><<<n_tokens, 32 * warps, inner * sizeof(float), s>>>(
+            walk, slices, (long long)n_tokens * inner, xbc, xbc_stride, D, proj + z_col, proj_stride, gain, eps, H, vdim, norm_groups, (float*)out);
+    else if (out_dtype == MLC_DTYPE_BF16)
+        state_space_finish_kernel<bf16><<<n_tokens, 32 * warps, inner * sizeof(float), s>>>(
+            walk, slices, (long long)n_tokens * inner, xbc, xbc_stride, D, proj + z_col, proj_stride, gain, eps, H, vdim, norm_groups, (bf16*)out);
+    else
+        return MLC_ERR_BAD_DTYPE;
+    MLC_LAUNCH_CHECK();
+    return 0;
 }

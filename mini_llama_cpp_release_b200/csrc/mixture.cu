@@ -74,7 +74,7 @@ __device__ __forceinline__ void route_logits(const TX* __restrict__ x, const flo
 template <typename TX, int PL>
 __global__ void __launch_bounds__(128)
 moe_route_kernel(const TX* __restrict__ x, const float* __restrict__ w, const float* __restrict__ bias, int n,
-                 int E, int K, int top, int* __restrict__ ids, float* __restrict__ weights) {
+                 int E, int K, int top, int weighting, int* __restrict__ ids, float* __restrict__ weights) {
     const int t = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     __shared__ float part[4][16];
@@ -118,6 +118,12 @@ moe_route_kernel(const TX* __restrict__ x, const float* __restrict__ w, const fl
         if (lane == j) mine = best;
         if (j == 0) first = best;                     // the largest: the softmax's reference point
         if (lane == 0) ids[(long long)t * top + j] = where == 0x7fffffff ? 0 : where;
+    }
+    if (weighting == 1) {
+        // every chosen expert's own sigmoid score, as it is (the sigmoid rises with the logit, so the largest scores are the
+        // largest logits)
+        if (lane < top) weights[(long long)t * top + lane] = 1.0f / (1.0f + expf(-mine));
+        return;
     }
     const float p = lane < top ? expf(mine - first) : 0.0f;
     const float sum = warp_sum(p);
@@ -366,11 +372,24 @@ grouped_linear_kernel(const TX* __restrict__ x, const int* __restrict__ src_tok,
 }
 
 // rows[r] = x[src_tok[r]] (zeros for padding), for products that want their operand dense
+// With `weights` (and row_of, top) a row is multiplied, in float32, by the weight of the (token, choice) pair it stands for:
+// the pair is the one of the row's token whose row_of names this row.
 template <typename T>
-__global__ void moe_gather_kernel(const T* __restrict__ x, const int* __restrict__ src_tok, int d, T* __restrict__ rows) {
+__global__ void moe_gather_kernel(const T* __restrict__ x, const int* __restrict__ src_tok, int d, T* __restrict__ rows,
+                                  const float* __restrict__ weights, const int* __restrict__ row_of, int top) {
     const int r = blockIdx.x;
     const int s = src_tok[r];
-    for (int i = threadIdx.x; i < d; i += blockDim.x) rows[(long long)r * d + i] = s >= 0 ? x[(long long)s * d + i] : from_float<T>(0.0f);
+    float w = 1.0f;
+    if (weights != nullptr && s >= 0) {
+        for (int j = 0; j < top; ++j)
+            if (row_of[(long long)s * top + j] == r) w = weights[(long long)s * top + j];
+    }
+    if (weights == nullptr) {
+        for (int i = threadIdx.x; i < d; i += blockDim.x) rows[(long long)r * d + i] = s >= 0 ? x[(long long)s * d + i] : from_float<T>(0.0f);
+    } else {
+        for (int i = threadIdx.x; i < d; i += blockDim.x)
+            rows[(long long)r * d + i] = from_float<T>(s >= 0 ? w * to_float(x[(long long)s * d + i]) : 0.0f);
+    }
 }
 
 // A negative row stands for the token's own input, `ident` [n][d] (TI), if given; else it adds nothing.
@@ -383,7 +402,7 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __res
         for (int j = 0; j < top; ++j) {
             const int r = row_of[(long long)t * top + j];
             const float e = r >= 0 ? y[(long long)r * d + i] : (ident != nullptr ? to_float(ident[(long long)t * d + i]) : 0.0f);
-            acc = fmaf(weights[(long long)t * top + j], e, acc);
+            acc = weights != nullptr ? fmaf(weights[(long long)t * top + j], e, acc) : acc + e;
         }
         out[(long long)t * d + i] = acc;
     }
@@ -460,15 +479,17 @@ __global__ void scaled_add_experts_kernel(float* __restrict__ x, const float* __
 using namespace mlc;
 
 // x: with w, the branch's input [n][K] of x_dtype (w float32 [E][K]); without w, the logits float32 [n][E] (K unused).
+// weighting 0: the softmax over the chosen logits; 1: the sigmoid of each chosen logit, not renormalised.
 extern "C" int mlc_moe_route(const void* x, int x_dtype, const float* w, const float* bias, int n, int E, int K, int top,
-                             int* ids, float* weights, void* stream) {
+                             int weighting, int* ids, float* weights, void* stream) {
     if (n <= 0) return 0;
+    if (weighting != 0 && weighting != 1) return MLC_ERR_UNSUPPORTED;
     if (E <= 0 || E > 32 * ROUTE_MAX_PER_LANE || top <= 0 || top > 32 || top > E || (w != nullptr && K <= 0)) return MLC_ERR_BAD_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
     if (w == nullptr || x_dtype == MLC_DTYPE_F32)
-        (E <= 32 ? moe_route_kernel<float, 1> : moe_route_kernel<float, ROUTE_MAX_PER_LANE>)<<<n, 128, 0, s>>>((const float*)x, w, bias, n, E, K, top, ids, weights);
+        (E <= 32 ? moe_route_kernel<float, 1> : moe_route_kernel<float, ROUTE_MAX_PER_LANE>)<<<n, 128, 0, s>>>((const float*)x, w, bias, n, E, K, top, weighting, ids, weights);
     else if (x_dtype == MLC_DTYPE_BF16)
-        (E <= 32 ? moe_route_kernel<bf16, 1> : moe_route_kernel<bf16, ROUTE_MAX_PER_LANE>)<<<n, 128, 0, s>>>((const bf16*)x, w, bias, n, E, K, top, ids, weights);
+        (E <= 32 ? moe_route_kernel<bf16, 1> : moe_route_kernel<bf16, ROUTE_MAX_PER_LANE>)<<<n, 128, 0, s>>>((const bf16*)x, w, bias, n, E, K, top, weighting, ids, weights);
     else
         return MLC_ERR_BAD_DTYPE;
     MLC_LAUNCH_CHECK();
@@ -533,15 +554,16 @@ extern "C" int mlc_grouped_linear(const void* x, int x_dtype, const int* src_tok
     return 0;
 }
 
-extern "C" int mlc_moe_gather(const void* x, int dtype, const int* src_tok, int max_rows, int d, void* rows, void* stream) {
+extern "C" int mlc_moe_gather(const void* x, int dtype, const int* src_tok, int max_rows, int d, void* rows, const float* weights,
+                              const int* row_of, int top, void* stream) {
     if (max_rows <= 0) return 0;
-    if (d <= 0) return MLC_ERR_BAD_SIZE;
+    if (d <= 0 || (weights != nullptr && (row_of == nullptr || top < 1))) return MLC_ERR_BAD_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = d >= 256 ? 256 : 64;
     if (dtype == MLC_DTYPE_F32)
-        moe_gather_kernel<float><<<max_rows, threads, 0, s>>>((const float*)x, src_tok, d, (float*)rows);
+        moe_gather_kernel<float><<<max_rows, threads, 0, s>>>((const float*)x, src_tok, d, (float*)rows, weights, row_of, top);
     else if (dtype == MLC_DTYPE_BF16)
-        moe_gather_kernel<bf16><<<max_rows, threads, 0, s>>>((const bf16*)x, src_tok, d, (bf16*)rows);
+        moe_gather_kernel<bf16><<<max_rows, threads, 0, s>>>((const bf16*)x, src_tok, d, (bf16*)rows, weights, row_of, top);
     else
         return MLC_ERR_BAD_DTYPE;
     MLC_LAUNCH_CHECK();

@@ -19,6 +19,7 @@ from ..config.model_config import ModelConfig
 from ..config.registry import build_model_spec, build_part
 from ..config.specs import ModelSpec
 from ..parts.base import CacheNeed, MixerMemory, Part, Runtime, StateSpec
+from ..parts.block import finish_deferred
 from ..weights.loader import load_weights
 from .step_info import StepInfo
 
@@ -120,7 +121,12 @@ class Model:
         for k, entry in enumerate(self.spec.schedule):
             memory = MixerMemory(kv=cache.view(k, step.page_tables), state=cache.state[k],
                                  writes_cache=entry.reads_cache_of is None)
-            x, pending = self.parts.blocks[entry.layer].forward(x, pending, step, memory)
+            block = self.parts.blocks[entry.layer]
+            if step.handover and not getattr(block, "takes_deferred_update", False):
+                finish_deferred(step)        # an update of the stream that the block before left for a block of its own kind
+            x, pending = block.forward(x, pending, step, memory)
+        if step.handover:
+            finish_deferred(step)
         n_want = step.want_rows.numel()
         if n_want == 0:
             return rt.empty(0, self.config.vocab_size, dtype=torch.float32)

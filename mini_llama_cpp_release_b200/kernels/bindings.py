@@ -20,6 +20,7 @@ __all__ = [
     "moe_route", "moe_plan", "moe_plan_rows", "grouped_linear", "moe_gather", "moe_combine", "scaled_add", "scaled_add_experts", "gla", "gla_slices", "latent_prepare",
     "head_project", "gemm_tcgen05_grouped", "GROUPED_TILE",
     "group_norm", "activation", "forget_gate_attention", "moe_route_scored",
+    "tanh_norm", "glu", "sigmoid_gate", "state_space",
 ]
 
 
@@ -94,7 +95,7 @@ def core() -> ctypes.CDLL:
             "mlc_add_rmsnorm": [P, P, I, P, F, I, I, P, I, P],
             "mlc_rope_table": [P, I, I, F, P, P],
             "mlc_layernorm": [P, P, I, P, F, I, I, I, P, I, P],
-            "mlc_qk_norm_rope_cache": [P, LL, I, I, I, P, P, F, P, P, P, I, I, I, I, I, I, I, I, F, P, I, P, P, P, LL, I, I, I, P],
+            "mlc_qk_norm_rope_cache": [P, LL, I, I, I, P, P, F, P, P, P, I, I, I, I, I, I, I, I, F, P, I, P, P, P, LL, I, I, I, P, P, P, I, I, P],
             "mlc_softcap": [P, LL, F, P],
             "mlc_causal_conv": [P, LL, P, P, P, I, I, I, P, LL, P, P, P, I, I, I, P, LL, P],
             "mlc_gated_delta_rule": [P, LL, I, I, I, P, LL, I, I, P, P, P, P, LL, P, P, I, I, I, I, I, I, I, P, P],
@@ -106,15 +107,19 @@ def core() -> ctypes.CDLL:
             "mlc_silu_mul": [P, I, I, I, I, P, I, P],
             "mlc_gather_rows": [P, P, I, LL, P, I, I, P, P, P],
             "mlc_convert": [P, I, LL, P, I, P],
-            "mlc_attention_simt": [P, P, I, P, P, I, I, I, I, I, I, F, I, I, P, P, P, P, P, LL, I, I, P, I, P],
-            "mlc_moe_route": [P, I, P, P, I, I, I, I, P, P, P],
+            "mlc_attention_simt": [P, P, I, P, P, I, I, I, I, I, I, F, I, I, P, P, P, P, P, LL, I, I, P, I, I, F, P],
+            "mlc_moe_route": [P, I, P, P, I, I, I, I, I, P, P, P],
             "mlc_moe_plan": [P, I, I, I, I, I, P, P, P, P],
             "mlc_grouped_linear": [P, I, P, P, I, P, I, I, I, I, P, I, P],
-            "mlc_moe_gather": [P, I, P, I, I, P, P],
+            "mlc_moe_gather": [P, I, P, I, I, P, P, P, I, P],
             "mlc_moe_combine": [P, P, P, P, I, I, I, I, P, P],
             "mlc_moe_route_scored": [P, I, P, P, I, I, I, I, I, I, F, P, P, P],
             "mlc_group_norm": [P, LL, I, I, I, P, I, F, F, P, I, P, P, P, I, P, I, P, LL, P, I, P, I, P],
             "mlc_activation": [P, I, LL, I, P, I, P],
+            "mlc_tanh_norm": [P, P, I, P, P, I, P, P, F, F, P, P, F, I, I, P, I, P],
+            "mlc_glu": [P, I, I, I, I, I, F, F, P, I, P],
+            "mlc_sigmoid_gate": [P, I, P, LL, I, I, I, I, P],
+            "mlc_state_space": [P, LL, I, I, P, LL, I, I, P, P, P, P, F, I, P, P, P, LL, P, P, I, I, I, I, I, I, I, P, P, I, P],
             "mlc_forget_gate_attention": [P, LL, I, I, I, P, P, P, P, P, LL, P, P, I, I, I, I, I, I, P, P],
             "mlc_scaled_add": [P, P, I, P, P, I, P, LL, I, P],
             "mlc_scaled_add_experts": [P, P, I, P, P, P, P, I, P, LL, I, P],
@@ -251,9 +256,11 @@ def qkv_post(qkv: torch.Tensor, bias: Optional[torch.Tensor], positions: torch.T
 def attention_simt(q: torch.Tensor, out: torch.Tensor, cu_seqlens: torch.Tensor, start_pos: torch.Tensor,
                    n_seqs: int, max_q_len: int, q_heads: int, kv: KVView, scale: float, window: int = 0,
                    n_splits: int = 1, part_ml: Optional[torch.Tensor] = None,
-                   part_o: Optional[torch.Tensor] = None, sinks: Optional[torch.Tensor] = None, keep_first: int = 0) -> None:
+                   part_o: Optional[torch.Tensor] = None, sinks: Optional[torch.Tensor] = None, keep_first: int = 0,
+                   chunk: int = 0, softcap: float = 0.0) -> None:
     """`sinks`: None, or float32 [q_heads]: exp(sinks[h]) joins the softmax denominator of head h (once, with no value).
-    `keep_first`: with a window, the sequence's first keys that stay visible at any distance."""
+    `keep_first`: with a window, the sequence's first keys that stay visible at any distance.  `chunk` > 0: position i sees
+    j <= i only from (i // chunk) * chunk on.  `softcap` > 0: score <- softcap * tanh(score / softcap)."""
     require_cuda(q, out, cu_seqlens, start_pos, part_ml, part_o, sinks)
     n_tokens = q.shape[0]
     assert q.dtype == out.dtype == kv.k_pool.dtype
@@ -265,7 +272,8 @@ def attention_simt(q: torch.Tensor, out: torch.Tensor, cu_seqlens: torch.Tensor,
                                      start_pos.data_ptr(), n_seqs, n_tokens, max_q_len, q_heads, kv.kv_heads,
                                      kv.head_dim, float(scale), int(window), n_splits, _ptr(part_ml), _ptr(part_o),
                                      kv.k_pool.data_ptr(), kv.v_pool.data_ptr(), kv.page_table.data_ptr(),
-                                     kv.entry_offset, kv.pages_per_seq, kv.page_size, _ptr(sinks), int(keep_first), _stream()),
+                                     kv.entry_offset, kv.pages_per_seq, kv.page_size, _ptr(sinks), int(keep_first), int(chunk),
+                                     float(softcap), _stream()),
            "attention")
     if n_splits > 1:
         count_launches(1)
@@ -383,12 +391,20 @@ def layernorm(x: torch.Tensor, y: Optional[torch.Tensor], gain: torch.Tensor, ep
 def qk_norm_rope_cache(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, q_gain: Optional[torch.Tensor],
                        k_gain: Optional[torch.Tensor], eps: float, positions: torch.Tensor, tok_seq: torch.Tensor,
                        rope: Optional[torch.Tensor], rot_dims: int, q_heads: int, kv_heads_in_row: int, dim: int, vdim: int,
-                       v_scale: float, q_out: torch.Tensor, kv: Optional[KVView]) -> None:
+                       v_scale: float, q_out: torch.Tensor, kv: Optional[KVView], q_bias: Optional[torch.Tensor] = None,
+                       k_bias: Optional[torch.Tensor] = None, v_bias: Optional[torch.Tensor] = None, whole_row: bool = False,
+                       interleaved: bool = False) -> None:
     """Rows of a float32 projection (q heads at column q_col, k heads at k_col, v heads at v_col): per-head RMS norm of q
     and k (gain optional; a negative eps: none), rotation of the first `rot_dims` entries of each head by the table
     `rope` [positions, rot_dims/2, 2], v times `v_scale`; q into q_out [n, q_heads, D], k and v into the cache, whose
-    heads have D >= max(dim, vdim) entries (the rest zero)."""
-    require_cuda(proj, q_gain, k_gain, positions, tok_seq, rope, q_out)
+    heads have D >= max(dim, vdim) entries (the rest zero).  Biases (float32, as long as their projections) are added as the
+    columns are read.  `whole_row`: one statistic over all q heads and one over all k heads, gains as long as the
+    projections.  `interleaved`: the rotation pairs entry 2j with 2j + 1 instead of j with j + rot_dims/2."""
+    require_cuda(proj, q_gain, k_gain, positions, tok_seq, rope, q_out, q_bias, k_bias, v_bias)
+    for g, heads in ((q_gain, q_heads), (k_gain, kv_heads_in_row)):
+        assert g is None or not heads or g.numel() == (heads * dim if whole_row else dim)
+    for b, size in ((q_bias, q_heads * dim), (k_bias, kv_heads_in_row * dim), (v_bias, kv_heads_in_row * vdim)):
+        assert b is None or not size or (b.dtype == torch.float32 and b.numel() == size)
     n = proj.shape[0]
     assert proj.dtype == torch.float32 and proj.dim() == 2
     D = q_out.numel() // max(1, n * q_heads)
@@ -404,7 +420,9 @@ def qk_norm_rope_cache(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, q
                                          float(eps), positions.data_ptr(), tok_seq.data_ptr(), _ptr(rope),
                                          rope.shape[0] if rope is not None else 0, rot_dims if rope is not None else 0, n,
                                          q_heads, kv_heads_in_row, dim, vdim, D, float(v_scale), q_out.data_ptr(),
-                                         dtype_code(q_out.dtype), *args, _stream()), "q/k norm, rotation and cache write")
+                                         dtype_code(q_out.dtype), *args, _ptr(q_bias), _ptr(k_bias), _ptr(v_bias),
+                                         1 if whole_row else 0, 1 if interleaved else 0, _stream()),
+           "q/k norm, rotation and cache write")
 
 
 def softcap(values: torch.Tensor, cap: float) -> None:
@@ -547,9 +565,9 @@ def gates_scan_step(u: torch.Tensor, w_r_t: torch.Tensor, w_i_t: torch.Tensor, b
 
 # ------------------------------------------------------------------ mixture of experts (csrc/mixture.cu)
 def moe_route(x: torch.Tensor, bias: Optional[torch.Tensor], top: int, ids: torch.Tensor, weights: torch.Tensor,
-              router: Optional[torch.Tensor] = None) -> None:
+              router: Optional[torch.Tensor] = None, weighting: str = "softmax") -> None:
     """Per token the `top` largest router logits (the lower index wins a tie) into ids int32 [n, top], and the softmax over
-    those chosen logits into weights float32 [n, top].  With `router` (float32 [E, K]) x is the branch's input [n, K] and
+    those chosen logits into weights float32 [n, top] (`weighting="sigmoid"`: each chosen logit's own sigmoid instead).  With `router` (float32 [E, K]) x is the branch's input [n, K] and
     the logits x · routerᵀ + bias are formed in float32 inside the kernel; without, x is the logits, float32 [n, E]."""
     require_cuda(x, bias, ids, weights, router)
     n = x.shape[0]
@@ -561,7 +579,8 @@ def moe_route(x: torch.Tensor, bias: Optional[torch.Tensor], top: int, ids: torc
         assert x.dtype == torch.float32
     assert ids.dtype == torch.int32 and weights.dtype == torch.float32
     assert ids.shape == (n, top) and weights.shape == (n, top) and (bias is None or (bias.dtype == torch.float32 and bias.numel() == E))
-    _check(core().mlc_moe_route(x.data_ptr(), dtype_code(x.dtype), _ptr(router), _ptr(bias), n, E, K, int(top), ids.data_ptr(),
+    _check(core().mlc_moe_route(x.data_ptr(), dtype_code(x.dtype), _ptr(router), _ptr(bias), n, E, K, int(top),
+                                {"softmax": 0, "sigmoid": 1}[weighting], ids.data_ptr(),
                                 weights.data_ptr(), _stream()), "expert routing")
 
 
@@ -599,23 +618,30 @@ def grouped_linear(x: torch.Tensor, src_tok: Optional[torch.Tensor], w: torch.Te
                                      _stream()), "grouped product")
 
 
-def moe_gather(x: torch.Tensor, src_tok: torch.Tensor, rows: torch.Tensor) -> None:
-    """rows[r] = x[src_tok[r]], zeros where src_tok[r] < 0."""
-    require_cuda(x, src_tok, rows)
+def moe_gather(x: torch.Tensor, src_tok: torch.Tensor, rows: torch.Tensor, weights: Optional[torch.Tensor] = None,
+               row_of: Optional[torch.Tensor] = None) -> None:
+    """rows[r] = x[src_tok[r]], zeros where src_tok[r] < 0.  With `weights` float32 [n, top] and `row_of` int32 [n, top], a row
+    is multiplied (float32) by the weight of the (token, choice) pair it stands for."""
+    require_cuda(x, src_tok, rows, weights, row_of)
     assert x.dtype == rows.dtype and rows.shape == (src_tok.numel(), x.shape[1])
+    top = 0
+    if weights is not None:
+        assert row_of is not None and weights.dtype == torch.float32 and row_of.dtype == torch.int32 and weights.shape == row_of.shape
+        top = row_of.shape[1]
     _check(core().mlc_moe_gather(x.data_ptr(), dtype_code(x.dtype), src_tok.data_ptr(), rows.shape[0], x.shape[1],
-                                 rows.data_ptr(), _stream()), "expert gather")
+                                 rows.data_ptr(), _ptr(weights), _ptr(row_of), top, _stream()), "expert gather")
 
 
-def moe_combine(y: torch.Tensor, row_of: torch.Tensor, weights: torch.Tensor, out: torch.Tensor,
+def moe_combine(y: torch.Tensor, row_of: torch.Tensor, weights: Optional[torch.Tensor], out: torch.Tensor,
                 ident: Optional[torch.Tensor] = None) -> None:
-    """out[t] = sum_j weights[t, j] · y[row_of[t, j]], float32, j in order.  A negative row stands for the token's own row of
+    """out[t] = sum_j weights[t, j] · y[row_of[t, j]], float32, j in order (without `weights`: the plain sum).  A negative row stands for the token's own row of
     `ident` [n, d] (an identity expert); without `ident` it adds nothing."""
     require_cuda(y, row_of, weights, out, ident)
     n, top = row_of.shape
-    assert y.dtype == out.dtype == weights.dtype == torch.float32 and out.shape == (n, y.shape[1])
+    assert y.dtype == out.dtype == torch.float32 and out.shape == (n, y.shape[1])
+    assert weights is None or weights.dtype == torch.float32
     assert ident is None or tuple(ident.shape) == tuple(out.shape)
-    _check(core().mlc_moe_combine(y.data_ptr(), row_of.data_ptr(), weights.data_ptr(), _ptr(ident),
+    _check(core().mlc_moe_combine(y.data_ptr(), row_of.data_ptr(), _ptr(weights), _ptr(ident),
                                   dtype_code(ident.dtype) if ident is not None else 0, n, top, y.shape[1], out.data_ptr(),
                                   _stream()), "expert combine")
 
@@ -719,6 +745,91 @@ def forget_gate_attention(proj: torch.Tensor, q_col: int, f_col: int, v_col: int
                                          step.slots.data_ptr(), step.cu_seqlens.data_ptr(), step.n_seqs, n, heads, dim, vdim, rows,
                                          out.data_ptr(), _stream()), "forget-gate linear attention")
     count_launches(1)
+
+
+def state_space(proj: torch.Tensor, z_col: int, dt_col: int, xbc: torch.Tensor, b_col: int, c_col: int, dt_bias: torch.Tensor,
+                A_log: torch.Tensor, D: torch.Tensor, gain: torch.Tensor, eps: float, norm_groups: int, state: torch.Tensor, step,
+                heads: int, groups: int, n_state: int, vdim: int, out: torch.Tensor) -> None:
+    """The state-space layer over the step's tokens (csrc/linear_attention.cu): dt = softplus(z_dt + dt_bias),
+    S <- exp(-exp(A_log) dt) S + dt B xT, y = ST C + D x per head (S [n_state, vdim]; head h reads B and C of group
+    h // (heads / groups)); then y · silu(z), an RMS norm in `norm_groups` equal parts, times `gain`.  The gate z (heads x vdim) and
+    the step logits (heads) in the float32 rows `proj`; x (heads x vdim, at column 0), B and C (groups x n_state each) in the
+    float32 rows `xbc`; state float32 [slots, heads*vdim*n_state]; out [n, heads*vdim] in the engine's type."""
+    require_cuda(dt_bias, A_log, D, gain, out)
+    _require_rows(state)
+    _require_rows(proj)
+    _require_rows(xbc)
+    n = proj.shape[0]
+    lib = core()
+    rows = lib.mlc_gla_rows(step.n_seqs, heads, n_state, vdim, _sm_count(out.device))
+    slices = (n_state + 8 * rows - 1) // (8 * rows)
+    inner = heads * vdim
+    assert state.shape[1] == inner * n_state and tuple(out.shape) == (n, inner) and gain.numel() == inner
+    for t in (dt_bias, A_log, D):
+        assert t.dtype == torch.float32 and t.numel() == heads
+    scratch = torch.empty(2 * n * heads + slices * n * inner, dtype=torch.float32, device=out.device)
+    dt, decay, walk = scratch[:n * heads], scratch[n * heads:2 * n * heads], scratch[2 * n * heads:]
+    _check(lib.mlc_state_space(proj.data_ptr(), proj.stride(0), z_col, dt_col, xbc.data_ptr(), xbc.stride(0), b_col, c_col,
+                               dt_bias.data_ptr(), A_log.data_ptr(), D.data_ptr(), gain.data_ptr(), float(eps), int(norm_groups),
+                               dt.data_ptr(), decay.data_ptr(), state.data_ptr(), state.stride(0), step.slots.data_ptr(),
+                               step.cu_seqlens.data_ptr(), step.n_seqs, n, heads, groups, n_state, vdim, rows, walk.data_ptr(),
+                               out.data_ptr(), dtype_code(out.dtype), _stream()), "state-space layer")
+    count_launches(2)
+
+
+# ------------------------------------------------------------------ dynamic tanh norm, gated units, sigmoid gate (csrc/tanh_norm.cu)
+def tanh_norm(x: torch.Tensor, y: Optional[torch.Tensor] = None, expert_rows=None, branch_norm=None, mult: float = 1.0,
+              next_norm=None, out: Optional[torch.Tensor] = None) -> None:
+    """Around the float32 stream x [n, d], with T(v) = tanh(a v) * w + b given as (a, w, b): if a branch is given (y float32
+    [n, d] or slices [s, n, d], or expert_rows = (rows float32 [., d], row_of int32 [n, top]): the plain sum of a token's
+    rows), x += mult * Tb(branch) in place (without `branch_norm`: mult * branch); if `next_norm` is given, out = Tn(x)."""
+    require_cuda(x, y, out)
+    n, d = x.shape
+    assert x.dtype == torch.float32 and x.is_contiguous()
+    n_slices = 1
+    if y is not None:
+        assert y.dtype == torch.float32 and tuple(y.shape[-2:]) == (n, d) and y.is_contiguous()
+        n_slices = y.shape[0] if y.dim() == 3 else 1
+    rows = row_of = None
+    top = 0
+    if expert_rows is not None:
+        rows, row_of = expert_rows
+        require_cuda(rows, row_of)
+        assert rows.dtype == torch.float32 and rows.shape[1] == d and row_of.dtype == torch.int32 and row_of.shape[0] == n
+        top = row_of.shape[1]
+    ba, bw, bb = branch_norm if branch_norm is not None else (0.0, None, None)
+    na, nw, nb = next_norm if next_norm is not None else (0.0, None, None)
+    for t in (bw, bb, nw, nb):
+        assert t is None or (t.dtype == torch.float32 and t.numel() == d and t.is_cuda)
+    assert (next_norm is None) == (out is None) and (out is None or tuple(out.shape) == (n, d))
+    _check(core().mlc_tanh_norm(x.data_ptr(), _ptr(y), n_slices, _ptr(rows), _ptr(row_of), top, _ptr(bw), _ptr(bb), float(ba),
+                                float(mult), _ptr(nw), _ptr(nb), float(na), n, d, _ptr(out),
+                                dtype_code(out.dtype) if out is not None else 0, _stream()), "tanh norm")
+
+
+GLU_KINDS = {"silu": 0, "gelu_tanh": 1, "clamped": 2}
+
+
+def glu(gate_up: torch.Tensor, out: torch.Tensor, kind: str, interleaved: bool = False, limit: float = 0.0,
+        alpha: float = 1.0) -> None:
+    """rows [gate | up] (or, interleaved, [g0, u0, g1, u1, ...]) -> act(gate) * up: "silu", "gelu_tanh", or "clamped":
+    g = min(gate, limit), u = clamp(up, -limit, limit), g * sigmoid(alpha * g) * (u + 1)."""
+    require_cuda(gate_up, out)
+    n, two_i = gate_up.shape
+    assert two_i % 2 == 0 and out.shape == (n, two_i // 2)
+    _check(core().mlc_glu(gate_up.data_ptr(), dtype_code(gate_up.dtype), n, two_i // 2, 1 if interleaved else 0, GLU_KINDS[kind],
+                          float(limit), float(alpha), out.data_ptr(), dtype_code(out.dtype), _stream()), "gated unit")
+
+
+def sigmoid_gate(o: torch.Tensor, gate: torch.Tensor, gate_col: int, heads: int, vdim: int) -> None:
+    """o [n, heads * D] (heads of D >= vdim entries) *= sigmoid(gate[:, gate_col + h * vdim + i]) on each head's first vdim
+    entries; gate float32 rows."""
+    require_cuda(o, gate)
+    n = o.shape[0]
+    D = o.shape[1] // heads
+    assert o.shape[1] == heads * D and D >= vdim and o.is_contiguous()
+    _check(core().mlc_sigmoid_gate(o.data_ptr(), dtype_code(o.dtype), _columns(gate, gate_col), gate.stride(0), n, heads, vdim, D,
+                                   _stream()), "sigmoid gate")
 
 
 # ------------------------------------------------------------------ norm in groups, activations (csrc/group_norm.cu)

@@ -1,2 +1,2 @@
 """Architectures.  Importing this package registers the built-in ones."""
-from . import qwen2, mepolix, kebesun, lonulix  # noqa: F401
+from . import qwen2, mepolix, kebesun, lonulix, nobonex  # noqa: F401

@@ -163,7 +163,9 @@ class GQAttention(Part):
         window = self.window or 0
         keep = getattr(self, "keep_first", 0) if window else 0     # first keys that stay visible beside the window
         sinks = getattr(self, "sinks", None)          # float32 [heads] or None: a logit per head that joins every softmax
-        if self.use_tensor_cores:
+        chunk = getattr(self, "chunk", None) or 0     # a mask of chunks instead of a window
+        softcap = getattr(self, "softcap", None) or 0.0
+        if self.use_tensor_cores and not chunk and not softcap:
             row_tiles, n_splits = kernels.attention_mma_plan(step.max_q_len, step.n_seqs, step.max_kv_len, self.H,
                                                              self.KV, rt.n_sms)
             if (step.max_q_len >= 16 and n_splits == 1
@@ -189,7 +191,8 @@ class GQAttention(Part):
             part_ml = rt.empty(q.shape[0] * self.H * n_splits * 2, dtype=torch.float32)
             part_o = rt.empty(q.shape[0] * self.H * n_splits * self.hd, dtype=torch.float32)
         kernels.attention_simt(q, o, step.cu_seqlens, step.start_pos, step.n_seqs, step.max_q_len, self.H, kv,
-                               self.scale, window, n_splits, part_ml, part_o, sinks=sinks, keep_first=keep)
+                               self.scale, window, n_splits, part_ml, part_o, sinks=sinks, keep_first=keep, chunk=chunk,
+                               softcap=softcap)
 
 
 def choose_splits(step, q_heads: int, kv_heads: int, n_sms: int, tokens_per_block: int, keys_per_split: int = 256,
@@ -230,20 +233,32 @@ class SinkAttention(GQAttention):
     the values as they are stored, which multiplies the attention's output (an arrangement that adds this mixer to
     another with a factor passes the factor here, so that it acts in float32 before anything is rounded).
 
-    `names`: the tensors' names below the part's prefix, by role (q, k, v, o, q_norm, k_norm, sink).  Offers
-    `in_weights()` and `mix()` to an arrangement that computes several mixers' input projections in one product."""
+    Options.  `bias`: q, k and v have biases (the tensor's name with `.b`), added in the projection, before the norm.
+    `softcap` c: score <- c · tanh(score / c) behind the scale.  `chunk` s: position i sees j <= i only if i // s == j // s,
+    chunks counted from the sequence's first position (instead of a window; the cache gives a chunk's pages back once the
+    sequence has left it).  `out_gate`: the heads' outputs are multiplied entry by entry by sigmoid(W_g h) before the output
+    product; W_g (`g`) reads the mixer's input and rides in the input product.  `own_kv=False`: the mixer has no key and value
+    tensors (projections, biases, key norm) and only ever reads another run's cache entry, with queries, mask and everything
+    else of its own.  The position part's `interleaved` says which entries form a rotation pair.
+
+    `names`: the tensors' names below the part's prefix, by role (q, k, v, o, q_norm, k_norm, sink, g; a bias is its matrix's
+    name with `.b`).  Offers `in_weights()` and `mix()` to an arrangement that computes several mixers' input projections in
+    one product."""
     graph_safe = True
     accumulates = False
 
-    NAMES = dict(q="q", k="k", v="v", o="o", q_norm="q.norm", k_norm="k.norm", sink="sink")
+    NAMES = dict(q="q", k="k", v="v", o="o", q_norm="q.norm", k_norm="k.norm", sink="sink", g="g")
 
     def __init__(self, name: str, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, v_head_dim: int,
                  scale: float, norm_eps: float, position: PartSpec, qk_norm: bool = True, sink: bool = True,
-                 window: Optional[int] = None, value_scale: float = 1.0, names: Optional[dict] = None, keep_first: int = 0):
+                 window: Optional[int] = None, value_scale: float = 1.0, names: Optional[dict] = None, keep_first: int = 0,
+                 bias: bool = False, softcap: Optional[float] = None, chunk: Optional[int] = None, out_gate: bool = False,
+                 own_kv: bool = True):
         """`window`, `keep_first`: position i sees j <= i with i - j < window or j < keep_first (no window: every j <= i)."""
         Part.__init__(self, name, hidden_size=hidden_size, num_heads=num_heads, num_kv_heads=num_kv_heads, head_dim=head_dim,
                       v_head_dim=v_head_dim, scale=scale, norm_eps=norm_eps, qk_norm=qk_norm, sink=sink, window=window,
-                      value_scale=value_scale, keep_first=keep_first)
+                      value_scale=value_scale, keep_first=keep_first, bias=bias, softcap=softcap, chunk=chunk, out_gate=out_gate,
+                      own_kv=own_kv)
         if num_heads % num_kv_heads:
             raise ValueError(f"attention: {num_heads} query heads are not a multiple of {num_kv_heads} kv heads")
         self.hidden, self.H, self.KV = int(hidden_size), int(num_heads), int(num_kv_heads)
@@ -258,34 +273,56 @@ class SinkAttention(GQAttention):
         self.window = int(window) if window else None
         self.keep_first = max(0, int(keep_first)) if self.window else 0
         self.value_scale = float(value_scale)
+        self.has_bias, self.out_gate, self.own_kv = bool(bias), bool(out_gate), bool(own_kv)
+        self.softcap = float(softcap) if softcap else None
+        self.chunk = int(chunk) if chunk else None
+        if self.softcap is not None and not self.softcap > 0:
+            raise ValueError(f"attention: the soft cap must be positive, got {softcap}")
+        if self.chunk is not None and (self.chunk < 1 or self.window):
+            raise ValueError("attention: a mask of chunks needs a positive size and excludes a window")
         self.t = {role: name + n for role, n in {**self.NAMES, **(names or {})}.items()}
         self.position = build_part(position, name)
-        if getattr(self.position, "interleaved", False):
-            raise ValueError("attention: this mixer's kernel rotates the pairs (i, i + dims/2) only")
+        self.interleaved = bool(getattr(self.position, "interleaved", False))
         self.sinks: Optional[torch.Tensor] = None
 
     def tensors(self):
         t = self.t
-        specs = [TensorSpec(t["q"], (self.H * self.dim, self.hidden)), TensorSpec(t["k"], (self.KV * self.dim, self.hidden)),
-                 TensorSpec(t["v"], (self.KV * self.vdim, self.hidden)), TensorSpec(t["o"], (self.hidden, self.H * self.vdim))]
+        specs = [TensorSpec(t["q"], (self.H * self.dim, self.hidden)), TensorSpec(t["o"], (self.hidden, self.H * self.vdim))]
+        if self.own_kv:
+            specs += [TensorSpec(t["k"], (self.KV * self.dim, self.hidden)), TensorSpec(t["v"], (self.KV * self.vdim, self.hidden))]
+        if self.has_bias:
+            specs.append(TensorSpec(t["q"] + ".b", (self.H * self.dim,), role="bias"))
+            if self.own_kv:
+                specs += [TensorSpec(t["k"] + ".b", (self.KV * self.dim,), role="bias"),
+                          TensorSpec(t["v"] + ".b", (self.KV * self.vdim,), role="bias")]
         if self.qk_norm:
-            specs += [TensorSpec(t["q_norm"], (self.dim,), role="gain", init="one_plus_normal"),
-                      TensorSpec(t["k_norm"], (self.dim,), role="gain", init="one_plus_normal")]
+            specs.append(TensorSpec(t["q_norm"], (self.dim,), role="gain", init="one_plus_normal"))
+            if self.own_kv:
+                specs.append(TensorSpec(t["k_norm"], (self.dim,), role="gain", init="one_plus_normal"))
         if self.has_sink:
             specs.append(TensorSpec(t["sink"], (self.H,), role="bias"))
+        if self.out_gate:
+            specs.append(TensorSpec(t["g"], (self.H * self.vdim, self.hidden)))
         return specs
 
     def cache_need(self) -> CacheNeed:
+        if self.chunk:
+            return CacheNeed("chunk", self.KV, self.hd, self.chunk)
         return CacheNeed("window" if self.window else "all", self.KV, self.hd, self.window, self.keep_first)
 
     def bind(self, get, runtime):
         Part.bind(self, get, runtime)
         t = self.t
-        self._in = [get(t["q"]), get(t["k"]), get(t["v"])]
+        f32 = lambda name: get(name).to(torch.float32).contiguous()
+        # columns of the input product: q | k | v | g (without the parts the mixer does not have)
+        self._in = [get(t["q"])] + ([get(t["k"]), get(t["v"])] if self.own_kv else []) + ([get(t["g"])] if self.out_gate else [])
         self.in_proj: Optional[Linear] = None
-        self.q_gain = get(t["q_norm"]).to(torch.float32).contiguous() if self.qk_norm else None
-        self.k_gain = get(t["k_norm"]).to(torch.float32).contiguous() if self.qk_norm else None
-        self.sinks = get(t["sink"]).to(torch.float32).contiguous() if self.has_sink else None
+        self.q_gain = f32(t["q_norm"]) if self.qk_norm else None
+        self.k_gain = f32(t["k_norm"]) if self.qk_norm and self.own_kv else None
+        self.q_bias = f32(t["q"] + ".b") if self.has_bias else None
+        self.k_bias = f32(t["k"] + ".b") if self.has_bias and self.own_kv else None
+        self.v_bias = f32(t["v"] + ".b") if self.has_bias and self.own_kv else None
+        self.sinks = f32(t["sink"]) if self.has_sink else None
         wo = get(t["o"])
         if self.hd != self.vdim:            # the kernels' heads are wider than the values: columns of zeros
             padded = torch.zeros(self.hidden, self.H, self.hd, dtype=wo.dtype, device=wo.device)
@@ -301,16 +338,19 @@ class SinkAttention(GQAttention):
         return list(self._in)
 
     def in_width(self) -> int:
-        return (self.H + self.KV) * self.dim + self.KV * self.vdim
+        return sum(w.shape[0] for w in self._in)
 
     def weight_bytes(self) -> int:
         return sum(w.numel() * w.element_size() for w in self._in) + self.o.nbytes()
 
     def mix(self, proj: torch.Tensor, col: int, step, memory: MixerMemory) -> torch.Tensor:
-        """Attention from the float32 projection rows `proj`, whose columns from `col` on are [q | k | v]; returns the
+        """Attention from the float32 projection rows `proj`, whose columns from `col` on are [q | k | v | g]; returns the
         heads' outputs [n, heads·D] in the engine's type, the input of `self.o`."""
         rt = self.runtime
         n = proj.shape[0]
+        if memory.writes_cache != self.own_kv:
+            raise ValueError("attention: a mixer without keys and values of its own reads another run's cache entry, and only "
+                             "such a mixer does")
         table = self.position.table_for(step.max_kv_len) if hasattr(self.position, "table_for") else None
         rot = getattr(self.position, "dims", 0) if table is not None else 0
         kv_heads = self.KV if memory.writes_cache else 0
@@ -318,11 +358,15 @@ class SinkAttention(GQAttention):
         q_col = col
         k_col = q_col + self.H * self.dim
         v_col = k_col + self.KV * self.dim
+        g_col = v_col + self.KV * self.vdim if self.own_kv else k_col
         kernels.qk_norm_rope_cache(proj, q_col, k_col, v_col, self.q_gain, self.k_gain, self.eps if self.qk_norm else -1.0,
                                    step.positions, step.tok_seq, table, rot, self.H, kv_heads, self.dim, self.vdim,
-                                   self.value_scale, q, memory.kv if memory.writes_cache else None)
+                                   self.value_scale, q, memory.kv if memory.writes_cache else None, q_bias=self.q_bias,
+                                   k_bias=self.k_bias, v_bias=self.v_bias, interleaved=self.interleaved)
         o = rt.empty(n, self.H * self.hd)
         self.attend(q, o, step, memory.kv)
+        if self.out_gate:
+            kernels.sigmoid_gate(o, proj, g_col, self.H, self.vdim)
         return o
 
     def forward(self, h: torch.Tensor, step, memory: MixerMemory, residual: Optional[torch.Tensor] = None):
@@ -472,3 +516,94 @@ class LatentAttention(GQAttention):
             self.in_proj = fused_rows(self._in, self.runtime)
         val = self.mix(self.in_proj(h, torch.float32), 0, step, memory)
         return self.o(val, torch.float32, partial_ok=True)
+
+
+@register_part("mixer", "conv_attention")
+class ConvKeyAttention(SinkAttention):
+    """Grouped-query attention whose queries and keys pass a short causal convolution over time, and whose values are the
+    convolved keys: there is no value matrix.
+
+        q = conv_q(W_q h),  k = conv_k(W_k h)        (per channel, `conv` taps, no bias; zeros before the sequence's start)
+        v = k, head by head, as it leaves the convolution
+        q <- rot(rms(q) · g_q),  k <- rot(rms(k) · g_k)   (rms over the whole projection, all heads at once; gains of that size)
+        out = W_o softmax(scale · q kᵀ, causal) v
+
+    Keys and values have the same head size.  State per sequence: the last conv-1 projected rows [q | k], float32; the
+    convolution's inputs and outputs are float32 in both engine modes.  No biases, no sink.  The position part's
+    `interleaved` says which entries form a rotation pair.  `names`: the tensors' names below the part's prefix, by role
+    (q, k, o, q_norm, k_norm, q_conv, k_conv)."""
+    graph_safe = True
+    accumulates = False
+
+    NAMES = dict(q="q", k="k", o="o", q_norm="q.norm", k_norm="k.norm", q_conv="q.conv", k_conv="k.conv")
+
+    def __init__(self, name: str, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
+                 norm_eps: float, conv: int, position: PartSpec, names: Optional[dict] = None):
+        SinkAttention.__init__(self, name, hidden_size=hidden_size, num_heads=num_heads, num_kv_heads=num_kv_heads,
+                               head_dim=head_dim, v_head_dim=head_dim, scale=scale, norm_eps=norm_eps, position=position,
+                               qk_norm=True, sink=False, names=names)
+        if conv < 1:
+            raise ValueError("attention: the convolution needs at least one tap")
+        self.taps = int(conv)
+        self.params["conv"] = self.taps
+        self.n_q, self.n_k = self.H * self.dim, self.KV * self.dim
+
+    def tensors(self):
+        t = self.t
+        return [TensorSpec(t["q"], (self.n_q, self.hidden)), TensorSpec(t["k"], (self.n_k, self.hidden)),
+                TensorSpec(t["o"], (self.hidden, self.n_q)),
+                TensorSpec(t["q_norm"], (self.n_q,), role="gain", init="one_plus_normal"),
+                TensorSpec(t["k_norm"], (self.n_k,), role="gain", init="one_plus_normal"),
+                TensorSpec(t["q_conv"], (self.n_q, self.taps)), TensorSpec(t["k_conv"], (self.n_k, self.taps))]
+
+    def state_spec(self):
+        from .base import StateSpec
+        return StateSpec(((self.taps - 1) * (self.n_q + self.n_k),), torch.float32) if self.taps > 1 else None
+
+    def bind(self, get, runtime):
+        Part.bind(self, get, runtime)
+        t = self.t
+        f32 = lambda name: get(name).to(torch.float32).contiguous()
+        self._in = [get(t["q"]), get(t["k"])]                     # columns of the input product: q | k
+        self.in_proj: Optional[Linear] = None
+        self.conv_w = torch.cat([f32(t["q_conv"]), f32(t["k_conv"])], dim=0).contiguous()
+        self.q_gain, self.k_gain = f32(t["q_norm"]), f32(t["k_norm"])
+        self.sinks = None
+        wo = get(t["o"])
+        if self.hd != self.dim:             # the kernels' heads are wider than the values: columns of zeros
+            padded = torch.zeros(self.hidden, self.H, self.hd, dtype=wo.dtype, device=wo.device)
+            padded[:, :, :self.dim] = wo.view(self.hidden, self.H, self.dim)
+            wo = padded.view(self.hidden, self.H * self.hd)
+        self.o = Linear(wo, runtime)
+        self.use_tensor_cores = runtime.dtype == torch.bfloat16
+        if self.use_tensor_cores:
+            kernels.attention_library(self.hd)
+        self._no_state: Optional[torch.Tensor] = None
+
+    def weight_bytes(self) -> int:
+        return sum(w.numel() * w.element_size() for w in self._in) + self.o.nbytes() + self.conv_w.numel() * 4
+
+    def mix(self, proj: torch.Tensor, col: int, step, memory: MixerMemory) -> torch.Tensor:
+        """Attention from the float32 projection rows `proj`, whose columns from `col` on are [q | k]; returns the heads'
+        outputs [n, heads·D] in the engine's type, the input of `self.o`."""
+        rt = self.runtime
+        n = proj.shape[0]
+        if not memory.writes_cache:
+            raise ValueError("attention: this mixer keeps its own keys")
+        qk = rt.empty(n, self.n_q + self.n_k, dtype=torch.float32)
+        state = memory.state
+        if state is None:                  # one tap: nothing is remembered
+            if self._no_state is None:
+                self._no_state = torch.zeros(1, 0, dtype=torch.float32, device=rt.device)
+            state = self._no_state
+        kernels.causal_conv(proj, col, self.conv_w, None, False, state, step, qk)
+        table = self.position.table_for(step.max_kv_len) if hasattr(self.position, "table_for") else None
+        rot = getattr(self.position, "dims", 0) if table is not None else 0
+        q = rt.empty(n, self.H * self.hd)
+        # the values are the key columns themselves, before norm and rotation
+        kernels.qk_norm_rope_cache(qk, 0, self.n_q, self.n_q, self.q_gain, self.k_gain, self.eps, step.positions, step.tok_seq,
+                                   table, rot, self.H, self.KV, self.dim, self.dim, 1.0, q, memory.kv, whole_row=True,
+                                   interleaved=self.interleaved)
+        o = rt.empty(n, self.H * self.hd)
+        self.attend(q, o, step, memory.kv)
+        return o

@@ -52,7 +52,9 @@ class TensorSpec:
 class CacheNeed:
     """Keys and values a mixer keeps per sequence.  kind "all": every position; "window":
     only the last `window` positions are ever read, and beside them the sequence's first
-    `keep_first` positions, which are never given back.  `shared_kv`: the values are read
+    `keep_first` positions, which are never given back; "chunk": a position reads only the
+    positions of its own chunk of `window` consecutive positions (chunks counted from the
+    sequence's start), so a chunk's pages are given back once the sequence has left it.  `shared_kv`: the values are read
     out of the key rows (their first entries), so the entry has one pool, not two."""
     kind: str
     kv_heads: int

@@ -313,3 +313,83 @@ class StreamMix(Part):
         both[:, :self.size].copy_(x)
         both[:, self.size:].copy_(e)
         return self.w(both, torch.float32), None
+
+
+class DeferredBranch:
+    """A branch output that a block left for whoever reads the stream next: x += mult · norm(branch) is still to be done.
+    The next block of the same kind does it inside its own first norm's kernel; anybody else calls `finish()`."""
+
+    def __init__(self, x: torch.Tensor, norm, mult: float, y: Optional[torch.Tensor] = None, expert_rows=None):
+        self.x, self.norm, self.mult, self.y, self.expert_rows = x, norm, mult, y, expert_rows
+
+    def finish(self) -> None:
+        self.norm.add_normed(self.x, y=self.y, expert_rows=self.expert_rows, mult=self.mult)
+
+
+DEFERRED = "deferred_update"          # the key under which a `DeferredBranch` waits in a step's `handover`
+
+
+def finish_deferred(step) -> None:
+    """Carry out the stream update a block may have left in the step's `handover`."""
+    left = step.handover.pop(DEFERRED, None)
+    if left is not None:
+        left.finish()
+
+
+@register_part("block", "sandwich")
+class SandwichBlock(Part):
+    """A norm before and a norm behind each branch: x <- x + m · Nb(mixer(Na(x))); x <- x + m · Nd(feed_forward(Nc(x))), with
+    m one number (`residual_mult`).  The feed-forward (with its two norms) may be absent.
+
+    The norms are of a kind that offers `add_normed(x, branch, mult, then)` and `triple()` (the elementwise tanh norm): the
+    addition of a normed branch and the norm that the next branch reads are one kernel.  The layer's last addition is left
+    in the step's `handover` as a `DeferredBranch` for the next block of this kind, whose first norm's kernel carries it
+    out; the model's step function finishes it where no such block follows (`takes_deferred_update`).  A mixture of experts
+    that defers its sum has its rows added up by the same kernel."""
+    graph_safe = True
+    takes_deferred_update = True
+
+    def __init__(self, name: str, mixer: PartSpec, mixer_norm: PartSpec, mixer_out_norm: PartSpec,
+                 feed_forward: Optional[PartSpec] = None, feed_forward_norm: Optional[PartSpec] = None,
+                 feed_forward_out_norm: Optional[PartSpec] = None, residual_mult: float = 1.0, names: Optional[dict] = None):
+        super().__init__(name, residual_mult=residual_mult)
+        names = names or {}
+        if not ((feed_forward is None) == (feed_forward_norm is None) == (feed_forward_out_norm is None)):
+            raise ValueError("sandwich block: a feed-forward and its two norms come together or not at all")
+        self.mult = float(residual_mult)
+
+        def make(spec, role):
+            return build_part(spec, name + names.get(role, role + ".")) if spec is not None else None
+        self.mixer_norm, self.mixer, self.mixer_out_norm = make(mixer_norm, "mixer_norm"), make(mixer, "mixer"), make(mixer_out_norm, "mixer_out_norm")
+        self.feed_forward_norm, self.feed_forward = make(feed_forward_norm, "feed_forward_norm"), make(feed_forward, "feed_forward")
+        self.feed_forward_out_norm = make(feed_forward_out_norm, "feed_forward_out_norm")
+        for norm in (self.mixer_norm, self.mixer_out_norm, self.feed_forward_norm, self.feed_forward_out_norm):
+            if norm is not None and not (hasattr(norm, "add_normed") and hasattr(norm, "triple")):
+                raise ValueError("sandwich block: its norms must offer `add_normed` and `triple`")
+
+    def children(self):
+        return tuple(p for p in (self.mixer_norm, self.mixer, self.mixer_out_norm, self.feed_forward_norm, self.feed_forward,
+                                 self.feed_forward_out_norm) if p is not None)
+
+    def forward(self, x: torch.Tensor, pending: Optional[torch.Tensor], step, memory: MixerMemory
+                ) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+        left = step.handover.pop(DEFERRED, None)
+        if left is not None and left.x is x and pending is None:
+            # the block before left its last addition: it and this block's first norm are one kernel
+            h = left.norm.add_normed(x, y=left.y, expert_rows=left.expert_rows, mult=left.mult, then=self.mixer_norm)
+        else:
+            if left is not None:
+                left.finish()
+            h = self.mixer_norm.forward(x, pending)
+        y = self.mixer.forward(h, step, memory)
+        ff = self.feed_forward
+        if ff is None:
+            step.handover[DEFERRED] = DeferredBranch(x, self.mixer_out_norm, self.mult, y=y)
+            return x, None
+        h = self.mixer_out_norm.add_normed(x, y=y, mult=self.mult, then=self.feed_forward_norm)
+        if getattr(ff, "defers_sum", False) and getattr(ff, "sum_is_plain", False):
+            rows, row_of, _ = ff.forward(h, step, deferred=True)
+            step.handover[DEFERRED] = DeferredBranch(x, self.feed_forward_out_norm, self.mult, expert_rows=(rows, row_of))
+        else:
+            step.handover[DEFERRED] = DeferredBranch(x, self.feed_forward_out_norm, self.mult, y=ff.forward(h, step))
+        return x, None

@@ -1,6 +1,7 @@
 """SwiGLU feed-forward: down( gate·sigmoid(gate)·up ), no biases
 (src/forward.cpp:672-702; src/ops.cpp:94-107).  Gate and up are one matrix product over
-[Wgate; Wup]; the activation and the product are one kernel."""
+[Wgate; Wup]; the activation and the product are one kernel.  With `activation="gelu_tanh"` the
+gate passes the tanh form of GELU instead (GEGLU)."""
 from __future__ import annotations
 
 from typing import Optional
@@ -27,8 +28,9 @@ class SwiGLU(Part):
         self.t_gate = name + names.get("gate", "gate_proj.weight")
         self.t_up = name + names.get("up", "up_proj.weight")
         self.t_down = name + names.get("down", "down_proj.weight")
-        if activation != "silu":
-            raise ValueError(f"feed-forward: only the silu activation is supported (src/ops.cpp:94-107), got {activation!r}")
+        if activation not in ("silu", "gelu_tanh"):
+            raise ValueError(f"feed-forward: the gate's activation is silu (src/ops.cpp:94-107) or gelu_tanh, got {activation!r}")
+        self.activation = activation
         self.hidden, self.inter = int(hidden_size), int(intermediate_size)
 
     def tensors(self):
@@ -60,7 +62,9 @@ class SwiGLU(Part):
     def forward(self, h: torch.Tensor, step=None, residual=None):
         rt = self.runtime
         a = rt.empty(h.shape[0], self.inter)
-        if self.fused and kernels.gemm_rows_takes(h.shape[0], 2 * self.inter, self.hidden):
+        if self.activation != "silu":
+            kernels.glu(self.gate_up(h, rt.dtype), a, self.activation, interleaved=self.fused)
+        elif self.fused and kernels.gemm_rows_takes(h.shape[0], 2 * self.inter, self.hidden):
             kernels.gemm_prompt(h, self.gate_up.weight, a, kernels.bindings.EPI_SILU_MUL, n_sms=rt.n_sms)    # prompts
         elif self.fused:
             kernels.gemm_tcgen05(h, self.gate_up.weight, a, kernels.bindings.EPI_SILU_MUL, n_sms=rt.n_sms)
@@ -86,6 +90,13 @@ class MixtureOfExperts(Part):
     score; one group: no grouping); the weights are s of the chosen (without the correction), divided by their sum
     + 1e-20, times `weight_scale`.  `identity`: that many further router outputs, behind the experts', belong to identity
     experts, which have no tensors and return their input; they take part in scores, groups and choice like the others.
+    `routing="sigmoid"`: s = sigmoid(z); chosen are the `top` largest; the weights are the chosen scores as they are.
+
+    `weight_on="input"`: a chosen expert's weight multiplies its input, not its output: the output is the plain sum of
+    expert(w · h) over the chosen (for experts that are not linear in their input this is another function).
+
+    Gated experts with `activation="clamped"` (`limit`, `act_alpha`): g = min(W_gate h, limit), u = clamp(W_up h, -limit,
+    limit), W_down (g · sigmoid(act_alpha · g) · (u + 1)).
 
     On the device and without a word to the host: the step's (token, expert) pairs are sorted by expert into runs that
     start on tile borders (`kernels.moe_plan`), every run's rows are multiplied by that expert's matrices, and each
@@ -102,26 +113,38 @@ class MixtureOfExperts(Part):
     def __init__(self, name: str, hidden_size: int, intermediate_size: int, num_experts: int, top: int,
                  router_bias: bool = True, names: Optional[dict] = None, gated: bool = True, activation: str = "silu",
                  routing: str = "top_logits", correction: bool = False, group_count: int = 1, group_keep: int = 1,
-                 identity: int = 0, weight_scale: float = 1.0):
+                 identity: int = 0, weight_scale: float = 1.0, weight_on: str = "output", limit: Optional[float] = None,
+                 act_alpha: float = 1.0):
         super().__init__(name, hidden_size=hidden_size, intermediate_size=intermediate_size, num_experts=num_experts, top=top,
                          router_bias=router_bias, gated=gated, activation=activation, routing=routing, correction=correction,
-                         group_count=group_count, group_keep=group_keep, identity=identity, weight_scale=weight_scale)
+                         group_count=group_count, group_keep=group_keep, identity=identity, weight_scale=weight_scale,
+                         weight_on=weight_on, limit=limit, act_alpha=act_alpha)
         self.hidden, self.inter, self.E, self.top = int(hidden_size), int(intermediate_size), int(num_experts), int(top)
         self.identity = int(identity)
         self.outputs = self.E + self.identity                     # what the router puts out
         if self.E < 1 or self.identity < 0 or not 1 <= self.top <= self.outputs or self.top > 32 or self.outputs > 256:
             raise ValueError(f"mixture of experts: top {top} of {num_experts} experts (+ {identity} identity experts) is not "
                              f"supported (top <= 32, router outputs <= 256)")
-        if routing not in ("top_logits", "scores"):
-            raise ValueError(f"mixture of experts: routing must be \"top_logits\" or \"scores\", got {routing!r}")
-        if activation not in kernels.bindings.ACTIVATIONS or (gated and activation != "silu"):
-            raise ValueError(f"mixture of experts: activation {activation!r} is not supported" + (" by gated experts" if gated else ""))
+        if routing not in ("top_logits", "scores", "sigmoid"):
+            raise ValueError(f"mixture of experts: routing must be \"top_logits\", \"scores\" or \"sigmoid\", got {routing!r}")
+        if gated and activation not in ("silu", "clamped"):
+            raise ValueError(f"mixture of experts: activation {activation!r} is not supported by gated experts")
+        if not gated and activation not in kernels.bindings.ACTIVATIONS:
+            raise ValueError(f"mixture of experts: activation {activation!r} is not supported")
+        if weight_on not in ("output", "input"):
+            raise ValueError(f"mixture of experts: weight_on must be \"output\" or \"input\", got {weight_on!r}")
+        self.limit, self.act_alpha = (float(limit) if limit is not None else 0.0), float(act_alpha)
+        if activation == "clamped" and not self.limit > 0:
+            raise ValueError(f"mixture of experts: clamped experts need a positive limit, got {limit}")
+        self.weight_on_input = weight_on == "input"
+        if self.weight_on_input and identity:
+            raise ValueError("mixture of experts: identity experts with weights on the input are not supported")
         self.gated, self.activation, self.routing = bool(gated), activation, routing
-        self.has_bias = bool(router_bias) and routing == "top_logits"
+        self.has_bias = bool(router_bias) and routing in ("top_logits", "sigmoid")
         self.has_correction = bool(correction)
         self.group_count, self.group_keep = max(1, int(group_count)), int(group_keep)
         self.weight_scale = float(weight_scale)
-        if routing == "top_logits" and (self.identity or self.has_correction or self.group_count > 1 or self.weight_scale != 1.0):
+        if routing != "scores" and (self.identity or self.has_correction or self.group_count > 1 or self.weight_scale != 1.0):
             raise ValueError("mixture of experts: identity experts, a correction, groups and a weight scale belong to routing=\"scores\"")
         if self.group_count > 1:
             if self.outputs % self.group_count or not 1 <= self.group_keep <= self.group_count:
@@ -160,6 +183,8 @@ class MixtureOfExperts(Part):
         # rows.  Otherwise float32 multiply-adds on [gate; up] with tiles of 64 rows.
         self.fused = (runtime.dtype == torch.bfloat16 and self.down.dtype == torch.bfloat16 and ups[0].dtype == torch.bfloat16
                       and self.hidden % 16 == 0 and self.inter % (8 if self.gated else 16) == 0)
+        # whether the gated product's epilogue applies the activation, or a kernel of its own behind a plain store
+        self.fused_act = self.activation == "silu"
         if not self.gated:
             self.gate_up = torch.stack(ups).contiguous()
         elif self.fused:
@@ -189,10 +214,17 @@ class MixtureOfExperts(Part):
             kernels.moe_route_scored(h, self.router, self.correction, self.top, self.group_count, self.group_keep,
                                      self.weight_scale, ids, weights)
         else:
-            kernels.moe_route(h, self.router_bias, self.top, ids, weights, router=self.router)   # logits, choice and weights in one kernel
+            # logits, choice and weights in one kernel
+            kernels.moe_route(h, self.router_bias, self.top, ids, weights, router=self.router,
+                              weighting="sigmoid" if self.routing == "sigmoid" else "softmax")
         return ids, weights
 
     defers_sum = True         # forward(..., deferred=True) may leave the weighted sum of a token's rows to the caller
+
+    @property
+    def sum_is_plain(self) -> bool:
+        """Whether the deferred sum is the plain sum of a token's rows (the weights already acted on the experts' inputs)."""
+        return self.weight_on_input
 
     def forward(self, h: torch.Tensor, step=None, residual=None, deferred: bool = False):
         """The mixture's output float32 [n, hidden]; with `deferred`, instead the pieces of its last step, (rows float32
@@ -210,18 +242,30 @@ class MixtureOfExperts(Part):
         kernels.moe_plan(ids, self.E, tile, row_of, src_tok, tile_expert)
         y = rt.empty(rows, self.hidden, dtype=torch.float32)
         act = rt.empty(rows, self.inter)
+        on_input = (weights, row_of) if self.weight_on_input else (None, None)
         if self.fused:
             hs = rt.empty(rows, self.hidden)
-            kernels.moe_gather(h, src_tok, hs)                       # the sorted rows, dense, as the product's TMA loads want them
-            if self.gated:
+            kernels.moe_gather(h, src_tok, hs, *on_input)            # the sorted rows, dense, as the product's TMA loads want them
+            if self.gated and not self.fused_act:
+                gu = rt.empty(rows, 2 * self.inter)
+                kernels.gemm_tcgen05_grouped(hs, self.gate_up, tile_expert, gu, kernels.bindings.EPI_STORE, n_sms=rt.n_sms)
+                kernels.glu(gu, act, self.activation, interleaved=True, limit=self.limit, alpha=self.act_alpha)
+            elif self.gated:
                 kernels.gemm_tcgen05_grouped(hs, self.gate_up, tile_expert, act, kernels.bindings.EPI_SILU_MUL, n_sms=rt.n_sms)
             else:
                 kernels.gemm_tcgen05_grouped(hs, self.gate_up, tile_expert, act, kernels.bindings.EPI_ACT[self.activation], n_sms=rt.n_sms)
             kernels.gemm_tcgen05_grouped(act, self.down, tile_expert, y, kernels.bindings.EPI_STORE, n_sms=rt.n_sms)
         else:
             gu = rt.empty(rows, (2 if self.gated else 1) * self.inter)
-            kernels.grouped_linear(h, src_tok, self.gate_up, tile_expert, tile, gu)
-            if self.gated:
+            if self.weight_on_input:
+                hs = rt.empty(rows, self.hidden)
+                kernels.moe_gather(h, src_tok, hs, *on_input)
+                kernels.grouped_linear(hs, None, self.gate_up, tile_expert, tile, gu)
+            else:
+                kernels.grouped_linear(h, src_tok, self.gate_up, tile_expert, tile, gu)
+            if self.gated and self.activation != "silu":
+                kernels.glu(gu, act, self.activation, limit=self.limit, alpha=self.act_alpha)
+            elif self.gated:
                 kernels.silu_mul(gu, act)
             else:
                 kernels.activation(gu, self.activation, act)
@@ -229,5 +273,5 @@ class MixtureOfExperts(Part):
         if deferred:
             return y, row_of, weights
         out = rt.empty(n, self.hidden, dtype=torch.float32)
-        kernels.moe_combine(y, row_of, weights, out, ident=h if self.identity else None)
+        kernels.moe_combine(y, row_of, None if self.weight_on_input else weights, out, ident=h if self.identity else None)
         return out

@@ -131,3 +131,54 @@ class GroupRMSNorm(Part):
         kernels.group_norm(x, self.groups, self.gain, self.eps, out=out, write_x=True, alpha=alpha, y=y, expert_rows=expert_rows,
                            gate=gate, gate_col=gate_col, gate_bias=gate_bias)
         return out
+
+
+@register_part("norm", "dynamic_tanh")
+class TanhNorm(Part):
+    """The elementwise norm T(v) = tanh(a · v) · w + b ("Dynamic Tanh"; Zhu, Chen, He, LeCun, Liu, "Transformers without
+    Normalization"): one stored number a, a gain w and a bias b per entry; no mean and no variance are taken.  Three uses:
+    `forward`, the norm of the stream (as `RMSNorm.forward`: adds `delta` first, as it is); `add_normed`, for arrangements
+    that norm a branch's output before it joins the stream, x += m · T(branch), optionally followed in the same kernel by
+    another norm of this kind on the new stream (the next part's input); `triple`, the norm as data for such a kernel.
+    `tensor` is the gain's name below the part's prefix; a and b are stored beside it as `<tensor>.alpha` and `<tensor>.b`."""
+    graph_safe = True
+
+    def __init__(self, name: str, size: int, tensor: str = "weight", alpha: str = ".alpha", bias: str = ".b"):
+        super().__init__(name, size=size, tensor=tensor, alpha=alpha, bias=bias)
+        self.size = int(size)
+        self.tensor = self.name + tensor
+        self.t_alpha, self.t_bias = self.tensor + alpha, self.tensor + bias
+
+    def tensors(self):
+        return [TensorSpec(self.tensor, (self.size,), role="gain", init="one_plus_normal"),
+                TensorSpec(self.t_bias, (self.size,), role="bias"),
+                TensorSpec(self.t_alpha, (), role="gain", init="one_plus_normal")]
+
+    def bind(self, get, runtime):
+        super().bind(get, runtime)
+        self.gain = get(self.tensor).to(torch.float32).contiguous()
+        self.bias = get(self.t_bias).to(torch.float32).contiguous()
+        self.alpha = float(get(self.t_alpha).to(torch.float32).reshape(-1)[0].item())     # read once, at load
+
+    def weight_bytes(self) -> int:
+        return (self.gain.numel() + self.bias.numel() + 1) * 4
+
+    def triple(self):
+        return (self.alpha, self.gain, self.bias)
+
+    def forward(self, x: torch.Tensor, delta: Optional[torch.Tensor] = None,
+                out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        """x: float32 [n, size], updated in place to x + delta when delta is given; returns T(x)."""
+        out = self.runtime.empty(*x.shape, dtype=out_dtype or self.runtime.dtype)
+        kernels.tanh_norm(x, y=delta, next_norm=self.triple(), out=out)
+        return out
+
+    def add_normed(self, x: torch.Tensor, y: Optional[torch.Tensor] = None, expert_rows=None, mult: float = 1.0,
+                   then: Optional["TanhNorm"] = None, out_dtype: Optional[torch.dtype] = None) -> Optional[torch.Tensor]:
+        """x (float32 [n, size], in place) += mult · T(branch); the branch is y (float32 [n, size], or slices that are added
+        up first) or expert_rows = (rows, row_of), the plain sum of each token's expert rows.  With `then`, also returns
+        then(x) of the new x in `out_dtype` (the engine's type by default)."""
+        out = self.runtime.empty(*x.shape, dtype=out_dtype or self.runtime.dtype) if then is not None else None
+        kernels.tanh_norm(x, y=y, expert_rows=expert_rows, branch_norm=self.triple(), mult=mult,
+                          next_norm=then.triple() if then is not None else None, out=out)
+        return out

@@ -425,3 +425,85 @@ class ParallelMixer(Part):
             out[0].copy_(lo(a_left, torch.float32))
             out[1].copy_(ro(a_right, torch.float32))
         return out
+
+
+@register_part("mixer", "state_space")
+class StateSpaceMixer(Part):
+    """The state-space layer of Mamba-2 (Dao and Gu, "Transformers are SSMs: Generalized Models and Efficient Algorithms
+    Through Structured State Space Duality").  With inner = heads x vdim, N = `state` and G = `groups`:
+
+        [z | x | B | C | dt] = W_in h          (inner | inner | G·N | G·N | heads)
+        [x | B | C] <- silu(conv([x | B | C]) + b_conv)     (causal, per channel, `conv` taps, the last one on the current token)
+        dt <- softplus(dt + dt_bias)           (no clamp)
+        per head n (group n // (heads / G)):  S_t = exp(-exp(A_log_n) dt) S_{t-1} + dt · B_t x_tᵀ;   y_t = S_tᵀ C_t + D_n x_t
+        out = W_o ( rms_parts(y · silu(z)) · w_norm )      (the gate first; then `norm_groups` equal parts of the row, each
+                                                            divided by its own root mean square)
+
+    State per sequence: S [heads, vdim, N] and the convolution's last conv-1 inputs, float32, zero at the start.  Step sizes,
+    decays, the convolution's outputs and the whole recurrence are float32 in both engine modes.  The walk over tokens is the
+    one of `GatedLinearAttention` (one decay per head instead of one per key channel; keys and queries shared by a group's
+    heads).  `names`: the tensors' names below the part's prefix, by role."""
+    graph_safe = True
+
+    NAMES = dict(w_in="in", conv="conv", conv_bias="conv.b", dt_bias="dt_bias", A_log="A_log", D="D", norm="norm", o="o")
+
+    def __init__(self, name: str, hidden_size: int, num_heads: int, v_head_dim: int, state: int, groups: int, conv: int,
+                 norm_eps: float, norm_groups: int = 1, names: Optional[dict] = None):
+        super().__init__(name, hidden_size=hidden_size, num_heads=num_heads, v_head_dim=v_head_dim, state=state, groups=groups,
+                         conv=conv, norm_eps=norm_eps, norm_groups=norm_groups)
+        self.hidden, self.H, self.vdim, self.N, self.G = int(hidden_size), int(num_heads), int(v_head_dim), int(state), int(groups)
+        self.taps, self.eps, self.norm_groups = int(conv), float(norm_eps), int(norm_groups)
+        if self.G < 1 or self.H % self.G:
+            raise ValueError(f"state-space layer: {num_heads} heads do not divide into {groups} groups")
+        if not 1 <= self.N <= 256:
+            raise ValueError(f"state-space layer: state sizes up to 256 are supported, got {state}")
+        if self.taps < 1:
+            raise ValueError("state-space layer: the convolution needs at least one tap")
+        self.inner = self.H * self.vdim
+        if self.norm_groups < 1 or self.inner % self.norm_groups:
+            raise ValueError(f"state-space layer: {self.inner} channels do not split into {norm_groups} equal parts")
+        if self.inner * 4 > 48 * 1024:
+            raise ValueError(f"state-space layer: up to 12288 inner channels are supported, got {self.inner}")
+        self.n_conv = self.inner + 2 * self.G * self.N                # channels that pass the convolution: x | B | C
+        self.n_S = self.inner * self.N
+        self.t = {role: name + n for role, n in {**self.NAMES, **(names or {})}.items()}
+
+    def tensors(self):
+        t = self.t
+        return [TensorSpec(t["w_in"], (2 * self.inner + 2 * self.G * self.N + self.H, self.hidden)),
+                TensorSpec(t["conv"], (self.n_conv, self.taps)), TensorSpec(t["conv_bias"], (self.n_conv,), role="bias"),
+                TensorSpec(t["dt_bias"], (self.H,), role="bias"), TensorSpec(t["A_log"], (self.H,), role="bias"),
+                TensorSpec(t["D"], (self.H,), role="gain", init="one_plus_normal"),
+                TensorSpec(t["norm"], (self.inner,), role="gain", init="one_plus_normal"),
+                TensorSpec(t["o"], (self.hidden, self.inner))]
+
+    def cache_need(self):
+        return None
+
+    def state_spec(self) -> StateSpec:
+        return StateSpec((self.n_S + (self.taps - 1) * self.n_conv,), torch.float32)
+
+    def bind(self, get, runtime):
+        super().bind(get, runtime)
+        t = self.t
+        self.in_proj = fused_rows([get(t["w_in"])], runtime)                  # columns: z | x | B | C | dt
+        self.conv_col = self.inner
+        self.dt_col = self.inner + self.n_conv
+        self.conv_w, self.conv_bias = _f32(get(t["conv"])), _f32(get(t["conv_bias"]))
+        self.dt_bias, self.A_log, self.D, self.gain = (_f32(get(t[r])) for r in ("dt_bias", "A_log", "D", "norm"))
+        self.o = Linear(get(t["o"]), runtime)
+
+    def weight_bytes(self) -> int:
+        return self.in_proj.nbytes() + self.o.nbytes() + self.conv_w.numel() * 4
+
+    def forward(self, h: torch.Tensor, step, memory: MixerMemory) -> torch.Tensor:
+        rt = self.runtime
+        n = h.shape[0]
+        proj = self.in_proj(h, torch.float32)
+        S, conv_state = memory.state[:, :self.n_S], memory.state[:, self.n_S:]
+        xbc = rt.empty(n, self.n_conv, dtype=torch.float32)
+        kernels.causal_conv(proj, self.conv_col, self.conv_w, self.conv_bias, True, conv_state, step, xbc)
+        act = rt.empty(n, self.inner)
+        kernels.state_space(proj, 0, self.dt_col, xbc, self.inner, self.inner + self.G * self.N, self.dt_bias, self.A_log, self.D,
+                            self.gain, self.eps, self.norm_groups, S, step, self.H, self.G, self.N, self.vdim, act)
+        return self.o(act, torch.float32, partial_ok=True)
