@@ -130,7 +130,12 @@ def _conv_attention(c: NobonexConfig, m: Dict[str, Any], where: str) -> PartSpec
         position=_rotation(m, where, "interleaved")))
 
 
-def _gated_attention(c: NobonexConfig, m: Dict[str, Any], where: str) -> PartSpec:
+def _mask_size(m: Dict[str, Any]) -> Optional[int]:
+    size = (m.get("mask") or {}).get("size")
+    return int(size) if size is not None else None
+
+
+def _gated_attention(c: NobonexConfig, m: Dict[str, Any], where: str, keep_all_keys: bool = False) -> PartSpec:
     mask = m.get("mask") or {}
     return PartSpec("mixer", "sink_attention", dict(
         hidden_size=c.hidden_size, num_heads=_count(m, "heads", where), num_kv_heads=_count(m, "kv_heads", where),
@@ -138,7 +143,7 @@ def _gated_attention(c: NobonexConfig, m: Dict[str, Any], where: str) -> PartSpe
         norm_eps=c.norm_eps, position=_rotation(m, where, "half"), qk_norm=True, sink=False, bias=True,
         softcap=_number(m, "softcap", where) if m.get("softcap") is not None else None,
         chunk=_count(mask, "size", where + ".mask") if mask.get("size") is not None else None,
-        out_gate=True, own_kv=m.get("kv_from") is None))
+        out_gate=True, own_kv=m.get("kv_from") is None, keep_all_keys=keep_all_keys))
 
 
 def _state_space(c: NobonexConfig, m: Dict[str, Any], where: str) -> PartSpec:
@@ -167,9 +172,15 @@ def nobonex(config: NobonexConfig) -> ModelSpec:
     builders = {"attention": _conv_attention, "attention_2": _gated_attention, "mamba2": _state_space}
     layers: List[LayerSpec] = []
     schedule: List[ScheduleEntry] = []
+    # a layer whose keys another layer reads under another mask keeps all of them: its own mask's chunks may end elsewhere
+    other_mask = {int(l["mixer"]["kv_from"]) for l in c.layers if l["mixer"].get("kv_from") is not None
+                  and _mask_size(l["mixer"]) != _mask_size(c.layers[int(l["mixer"]["kv_from"])]["mixer"])}
     for i, layer in enumerate(c.layers):
+        where = f"layers[{i}].mixer"
+        mixer = (_gated_attention(c, layer["mixer"], where, keep_all_keys=i in other_mask) if layer["type"] == "attention_2"
+                 else builders[layer["type"]](c, layer["mixer"], where))
         params: Dict[str, Any] = dict(
-            mixer=builders[layer["type"]](c, layer["mixer"], f"layers[{i}].mixer"), mixer_norm=norm("norm1"),
+            mixer=mixer, mixer_norm=norm("norm1"),
             mixer_out_norm=norm("norm1b"), residual_mult=c.residual_mult,
             names={"mixer": "mix.", "mixer_norm": "", "mixer_out_norm": "", "feed_forward": "mlp.", "feed_forward_norm": "",
                    "feed_forward_out_norm": ""})

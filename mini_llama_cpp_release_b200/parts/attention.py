@@ -239,7 +239,8 @@ class SinkAttention(GQAttention):
     sequence has left it).  `out_gate`: the heads' outputs are multiplied entry by entry by sigmoid(W_g h) before the output
     product; W_g (`g`) reads the mixer's input and rides in the input product.  `own_kv=False`: the mixer has no key and value
     tensors (projections, biases, key norm) and only ever reads another run's cache entry, with queries, mask and everything
-    else of its own.  The position part's `interleaved` says which entries form a rotation pair.
+    else of its own.  `keep_all_keys`: the cache keeps every position whatever this mixer's own mask (for an entry that
+    another run reads under another mask).  The position part's `interleaved` says which entries form a rotation pair.
 
     `names`: the tensors' names below the part's prefix, by role (q, k, v, o, q_norm, k_norm, sink, g; a bias is its matrix's
     name with `.b`).  Offers `in_weights()` and `mix()` to an arrangement that computes several mixers' input projections in
@@ -253,12 +254,12 @@ class SinkAttention(GQAttention):
                  scale: float, norm_eps: float, position: PartSpec, qk_norm: bool = True, sink: bool = True,
                  window: Optional[int] = None, value_scale: float = 1.0, names: Optional[dict] = None, keep_first: int = 0,
                  bias: bool = False, softcap: Optional[float] = None, chunk: Optional[int] = None, out_gate: bool = False,
-                 own_kv: bool = True):
+                 own_kv: bool = True, keep_all_keys: bool = False):
         """`window`, `keep_first`: position i sees j <= i with i - j < window or j < keep_first (no window: every j <= i)."""
         Part.__init__(self, name, hidden_size=hidden_size, num_heads=num_heads, num_kv_heads=num_kv_heads, head_dim=head_dim,
                       v_head_dim=v_head_dim, scale=scale, norm_eps=norm_eps, qk_norm=qk_norm, sink=sink, window=window,
                       value_scale=value_scale, keep_first=keep_first, bias=bias, softcap=softcap, chunk=chunk, out_gate=out_gate,
-                      own_kv=own_kv)
+                      own_kv=own_kv, keep_all_keys=keep_all_keys)
         if num_heads % num_kv_heads:
             raise ValueError(f"attention: {num_heads} query heads are not a multiple of {num_kv_heads} kv heads")
         self.hidden, self.H, self.KV = int(hidden_size), int(num_heads), int(num_kv_heads)
@@ -274,6 +275,7 @@ class SinkAttention(GQAttention):
         self.keep_first = max(0, int(keep_first)) if self.window else 0
         self.value_scale = float(value_scale)
         self.has_bias, self.out_gate, self.own_kv = bool(bias), bool(out_gate), bool(own_kv)
+        self.keep_all_keys = bool(keep_all_keys)
         self.softcap = float(softcap) if softcap else None
         self.chunk = int(chunk) if chunk else None
         if self.softcap is not None and not self.softcap > 0:
@@ -306,6 +308,8 @@ class SinkAttention(GQAttention):
         return specs
 
     def cache_need(self) -> CacheNeed:
+        if self.keep_all_keys:              # another run reads this entry under a mask of its own
+            return CacheNeed("all", self.KV, self.hd)
         if self.chunk:
             return CacheNeed("chunk", self.KV, self.hd, self.chunk)
         return CacheNeed("window" if self.window else "all", self.KV, self.hd, self.window, self.keep_first)
