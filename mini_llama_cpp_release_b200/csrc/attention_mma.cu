@@ -51,6 +51,9 @@ struct MmaArgs {
     int group;
     int window;
     int keep_first;           // with a window: the sequence's first keys that stay visible at any distance
+    int chunk;                // > 0 (and no window): position p reads the keys from (p / chunk) * chunk on
+    float cap_over_scale;     // a soft cap c on the scaled scores, carried as c / scale and scale / c (0: none): the raw score s
+    float scale_over_cap;     // becomes (c / scale) tanh(s scale / c), and the scale goes on riding in the exponent
     int tokens_per_block;
     int heads_per_block;
     int head_chunks;
@@ -61,6 +64,15 @@ struct MmaArgs {
     unsigned long long* stamps;   // decode kernel: null, or [blocks][12] nanosecond stamps of each block's phases
     int* status;              // decode kernel with TMA loads: where a wait that ran out leaves its code (31)
 };
+
+// The first key position p reads: its chunk's first, its window's first, or the sequence's first.  Never decreases with p.
+__device__ __forceinline__ int first_key_of(const MmaArgs& a, int p) {
+    return a.chunk > 0 ? (p / a.chunk) * a.chunk : (a.window > 0 ? max(0, p - a.window + 1) : 0);
+}
+
+// tanh to float32 rounding of its value near zero and beyond (1 - 2 / (1 + e^2x) would cancel near zero)
+__device__ __forceinline__ float soft_cap_raw(const MmaArgs& a, float s) { return a.cap_over_scale * tanhf(s * a.scale_over_cap); }
+
 
 __device__ __forceinline__ unsigned long long stamp_ns() {
     unsigned long long t;
@@ -149,7 +161,7 @@ attention_mma_kernel(MmaArgs a, PagedKV c) {
 
     // ---- key range of the block and of this split, in tiles
     const int p_first = start + tok0, p_last = start + tok0 + n_tok - 1;
-    const int lo_block = (a.window > 0) ? max(0, p_first - a.window + 1) : 0;
+    const int lo_block = first_key_of(a, p_first);
     const int tile_begin = lo_block / TILE, tile_end = p_last / TILE + 1;
     // Tiles of kept first keys that lie before the window's first tile are walked ahead of it: the walk's tile number v
     // stands for tile v below `head_tiles` and for tile_begin + (v - head_tiles) from there on (`tile_of`).  my_begin
@@ -197,15 +209,15 @@ attention_mma_kernel(MmaArgs a, PagedKV c) {
         const int t = r / GH, hg = chunk * GH + r % GH;
         row_ok[e] = (t < n_tok) && (hg < a.group);
         row_hi[e] = row_ok[e] ? start + tok0 + t : -1;
-        row_lo[e] = (a.window > 0) ? max(0, row_hi[e] - a.window + 1) : 0;
+        row_lo[e] = first_key_of(a, max(row_hi[e], 0));
     }
     // the warp's rows span these positions (rows are ordered by token)
     const int warp_t_first = (rt * 16) / GH, warp_t_last = min((rt * 16 + 15) / GH, n_tok - 1);
     const int warp_hi = start + tok0 + warp_t_last;
-    const int warp_lo = (a.window > 0) ? max(0, start + tok0 + warp_t_first - a.window + 1) : 0;
+    const int warp_lo = first_key_of(a, start + tok0 + warp_t_first);
     const bool warp_has_rows = warp_t_first < n_tok;
     const int warp_first_pos = start + tok0 + warp_t_first;                       // keys up to here are visible to every row of the warp
-    const int warp_lo_last = (a.window > 0) ? max(0, warp_hi - a.window + 1) : 0;   // keys from here on are inside every row's window
+    const int warp_lo_last = first_key_of(a, max(warp_hi, 0));   // keys from here on are inside every row's window
 
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
     float o[NT_O][4];
@@ -259,6 +271,12 @@ attention_mma_kernel(MmaArgs a, PagedKV c) {
                     mma_bf16(s[2 * jp], af, bfr[0], bfr[1]);
                     mma_bf16(s[2 * jp + 1], af, bfr[2], bfr[3]);
                 }
+            }
+            if (a.cap_over_scale > 0.0f) {
+#pragma unroll
+                for (int j = 0; j < NT_S; ++j)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) s[j][e] = soft_cap_raw(a, s[j][e]);
             }
             // mask (only where the tile meets the diagonal, a window's edge or the sequence's end), running maximum.
             // Scores stay unscaled; the scale rides in the exponent's multiply-add.
@@ -514,7 +532,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     if (tok0 >= q_len) return;
     const int n_tok = min(a.tokens_per_block, q_len - tok0);
     const int p_first = start + tok0, p_last = start + tok0 + n_tok - 1;
-    const int lo_block = (a.window > 0) ? max(0, p_first - a.window + 1) : 0;
+    const int lo_block = first_key_of(a, p_first);
     const int tile_begin = lo_block / TILE, tile_end = p_last / TILE + 1;          // in 64-key pages
     // pages of kept first keys before the window's first page are walked ahead of it; my_begin, my_end and the sub-tile
     // numbers below count along that walk, `real_st` gives a walk number's true sub-tile
@@ -631,10 +649,10 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         const int t = r / GH, hg = chunk * GH + r % GH;
         row_ok[e] = (t < n_tok) && (hg < a.group);
         row_hi[e] = row_ok[e] ? start + tok0 + t : -1;
-        row_lo[e] = (a.window > 0) ? max(0, row_hi[e] - a.window + 1) : 0;
+        row_lo[e] = first_key_of(a, max(row_hi[e], 0));
     }
     all_hi = start + tok0;                                                           // the first token's position
-    all_lo = (a.window > 0) ? max(0, p_last - a.window + 1) : 0;                     // the last token's window start
+    all_lo = first_key_of(a, p_last);                     // the last token's window start
 
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
     float o[NT_O][4];
@@ -703,6 +721,12 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                     mma_bf16(sc[2 * jp], af, bfr[0], bfr[1]);
                     mma_bf16(sc[2 * jp + 1], af, bfr[2], bfr[3]);
                 }
+            }
+            if (a.cap_over_scale > 0.0f) {
+#pragma unroll
+                for (int j = 0; j < D_NT_S; ++j)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) sc[j][e] = soft_cap_raw(a, sc[j][e]);
             }
             float mx[2] = {-INFINITY, -INFINITY};
             const bool all_visible = (key0 >= all_lo || key0 + DKT <= keep) && key0 + DKT - 1 <= all_hi;       // the same for the whole warp
@@ -1032,9 +1056,10 @@ extern "C" int mlc_attention_mma(const void* q, void* out, const int* cu_seqlens
                                  int window, int row_tiles, int warp_private, int n_splits, float* part_ml, float* part_o,
                                  void* k_pool, void* v_pool, const int* page_table, long long entry_offset,
                                  int pages_per_seq, int page_size, int pool_pages, int* status, const float* sinks,
-                                 int keep_first, void* stream) {
+                                 int keep_first, int chunk, float softcap, void* stream) {
     if (n_seqs <= 0 || n_tokens <= 0) return 0;
     if (hd != HD || page_size != TILE) return MLC_ERR_BAD_SIZE;
+    if (chunk < 0 || (chunk > 0 && window > 0) || softcap < 0.0f) return MLC_ERR_UNSUPPORTED;
     if (q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads != 0 || n_seqs > 65535) return MLC_ERR_BAD_SIZE;
     if (row_tiles != 1 && row_tiles != 2 && row_tiles != 4) return MLC_ERR_BAD_SIZE;
     if (!(scale > 0.0f)) return MLC_ERR_BAD_SIZE;                     // the kernels move the scale past a maximum
@@ -1056,6 +1081,9 @@ extern "C" int mlc_attention_mma(const void* q, void* out, const int* cu_seqlens
     a.group = q_heads / kv_heads;
     a.window = window;
     a.keep_first = keep_first < 0 ? 0 : keep_first;
+    a.chunk = chunk;
+    a.cap_over_scale = softcap > 0.0f ? softcap / scale : 0.0f;
+    a.scale_over_cap = softcap > 0.0f ? scale / softcap : 0.0f;
     const int rows = 16 * row_tiles;
     a.heads_per_block = a.group < rows ? a.group : rows;
     a.tokens_per_block = rows / a.heads_per_block;

@@ -56,6 +56,9 @@ struct TcAttnArgs {
     int heads_per_block, tokens_per_block, head_chunks;
     int window;
     int keep_first;           // with a window: the sequence's first keys that stay visible at any distance
+    int chunk;                // > 0 (and no window): position p reads the keys from (p / chunk) * chunk on
+    float cap_over_scale;     // a soft cap c on the scaled scores, carried as c / scale and 2 log2(e) scale / c (0: none): the raw
+    float cap_exponent;       // score s becomes (c / scale) tanh(s scale / c), and the scale goes on riding in the exponent
     float scale_log2;
     const float* sinks;         // [q_heads] or null: exp(sinks[h]) joins head h's softmax denominator once, with no value
     int* status;
@@ -162,7 +165,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     const int n_tok = min(a.tokens_per_block, q_len - tok0);          // <= 0: nothing to do for this block
     const int start = a.start_pos[b];
     const int p_first = start + tok0, p_last = start + tok0 + n_tok - 1;
-    const int lo_block = (a.window > 0) ? max(0, p_first - a.window + 1) : 0;
+    const int lo_block = a.chunk > 0 ? (p_first / a.chunk) * a.chunk : (a.window > 0) ? max(0, p_first - a.window + 1) : 0;
     const int tile_begin = lo_block / A_BN;
     // tiles of kept first keys before the window's first tile are walked ahead of it: walk number j stands for tile j
     // below `head_tiles` and for tile_begin + (j - head_tiles) from there on
@@ -283,7 +286,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         // Rows that do not exist take the range of the block's last token: they then mask exactly when their neighbours
         // do, whatever lies in their part of the query tile, and nothing of theirs is stored.
         const int hi = start + tok0 + min(t, n_tok - 1);
-        const int lo = (a.window > 0) ? max(0, hi - a.window + 1) : 0;
+        const int lo = a.chunk > 0 ? (hi / a.chunk) * a.chunk : (a.window > 0) ? max(0, hi - a.window + 1) : 0;
         const unsigned lane_base = (unsigned)(q4 * 32) << 16;
         // m is the maximum the row's probabilities and output are scaled by.  It follows the true maximum lazily: only
         // when a tile's maximum exceeds it by more than 8 (probabilities up to 2^8, harmless in float32 and bfloat16)
@@ -317,6 +320,13 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             float sc[A_BN];
             static_assert(A_BN == 64, "one load of 64 columns");
             tmem_load64(s_taddr, sc);
+            if (a.cap_over_scale > 0.0f) {
+                // tanh(x) = 1 - 2 / (1 + e^2x): exact to float32 rounding of one, which is what a probability rounded to 16
+                // bits can show; e^2x = inf gives 1, e^2x = 0 gives -1
+#pragma unroll
+                for (int c = 0; c < A_BN; ++c)
+                    sc[c] = a.cap_over_scale * (1.0f - __fdividef(2.0f, 1.0f + fast_exp2(sc[c] * a.cap_exponent)));
+            }
             if (masked) {
 #pragma unroll
                 for (int c = 0; c < A_BN; ++c) {
@@ -484,8 +494,9 @@ extern "C" int mlc_attention_tcgen05(const void* q, void* out, const int* cu_seq
                                      int n_tokens, int max_q_len, int q_heads, int kv_heads, int hd, float scale, int window,
                                      int* status, void* k_pool, void* v_pool, const int* page_table, long long entry_offset,
                                      int pages_per_seq, int page_size, long long pool_pages, long long* timing, const float* sinks,
-                                     int keep_first, void* stream) {
+                                     int keep_first, int chunk, float softcap, void* stream) {
 #if MLC_ATTENTION_TCGEN05
+    if (chunk < 0 || (chunk > 0 && window > 0) || softcap < 0.0f) return MLC_ERR_UNSUPPORTED;
     if (hd != A_HD || page_size != A_BN) return MLC_ERR_UNSUPPORTED;
     if (n_seqs <= 0 || n_tokens <= 0 || max_q_len <= 0) return 0;
     if (q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads != 0 || status == nullptr || pool_pages <= 0) return MLC_ERR_BAD_SIZE;
@@ -506,6 +517,9 @@ extern "C" int mlc_attention_tcgen05(const void* q, void* out, const int* cu_seq
     a.head_chunks = (group + a.heads_per_block - 1) / a.heads_per_block;
     a.window = window;
     a.keep_first = keep_first < 0 ? 0 : keep_first;
+    a.chunk = chunk;
+    a.cap_over_scale = softcap > 0.0f ? softcap / scale : 0.0f;
+    a.cap_exponent = softcap > 0.0f ? 2.0f * 1.4426950408889634f * scale / softcap : 0.0f;
     a.scale_log2 = scale * 1.4426950408889634f;
     a.status = status;
     a.sinks = sinks;

@@ -970,12 +970,12 @@ def attention_library(head_dim: int) -> ctypes.CDLL:
     if lib is None:
         lib = _build.attention_library(head_dim)
         P, I, F, LL = c_void_p, c_int, c_float, c_longlong
-        lib.mlc_attention_mma.argtypes = [P, P, P, P, I, I, I, I, I, I, F, I, I, I, I, P, P, P, P, P, LL, I, I, I, P, P, I, P]
+        lib.mlc_attention_mma.argtypes = [P, P, P, P, I, I, I, I, I, I, F, I, I, I, I, P, P, P, P, P, LL, I, I, I, P, P, I, I, F, P]
         lib.mlc_attention_mma.restype = c_int
         lib.mlc_attention_mma_head_dim.restype = c_int
         lib.mlc_attention_decode_clusters_resident.argtypes = [I]
         lib.mlc_attention_decode_clusters_resident.restype = c_int
-        lib.mlc_attention_tcgen05.argtypes = [P, P, P, P, I, I, I, I, I, I, F, I, P, P, P, P, LL, I, I, LL, P, P, I, P]
+        lib.mlc_attention_tcgen05.argtypes = [P, P, P, P, I, I, I, I, I, I, F, I, P, P, P, P, LL, I, I, LL, P, P, I, I, F, P]
         lib.mlc_attention_tcgen05.restype = c_int
         if lib.mlc_attention_mma_head_dim() != head_dim:
             raise KernelError(f"attention library built for head size {lib.mlc_attention_mma_head_dim()}, wanted {head_dim}")
@@ -1053,7 +1053,7 @@ def attention_tcgen05_blocks(max_q_len: int, n_seqs: int, q_heads: int, kv_heads
 
 def attention_tcgen05(q: torch.Tensor, out: torch.Tensor, cu_seqlens: torch.Tensor, start_pos: torch.Tensor, n_seqs: int,
                       max_q_len: int, q_heads: int, kv: KVView, scale: float, window: int,
-                      sinks: Optional[torch.Tensor] = None, keep_first: int = 0) -> None:
+                      sinks: Optional[torch.Tensor] = None, keep_first: int = 0, chunk: int = 0, softcap: float = 0.0) -> None:
     """Prompt attention of bfloat16 q [n, q_heads*hd] over a bfloat16 cache entry on the tcgen05 tensor cores
     (head sizes 64 and 128, pages of 64 tokens).  Keys are not shared out over blocks: meant for steps whose rows fill
     the GPU; a block itself works on two key tiles at a time."""
@@ -1067,16 +1067,17 @@ def attention_tcgen05(q: torch.Tensor, out: torch.Tensor, cu_seqlens: torch.Tens
                                      q.shape[0], max_q_len, q_heads, kv.kv_heads, kv.head_dim, float(scale), int(window),
                                      status.data_ptr(), kv.k_pool.data_ptr(), kv.v_pool.data_ptr(), kv.page_table.data_ptr(),
                                      kv.entry_offset, kv.pages_per_seq, kv.page_size, kv.k_pool.shape[1], None, _ptr(sinks),
-                                     int(keep_first), _stream()),
+                                     int(keep_first), int(chunk), float(softcap), _stream()),
            "tcgen05 attention")
 
 
 def attention_mma(q: torch.Tensor, out: torch.Tensor, cu_seqlens: torch.Tensor, start_pos: torch.Tensor, n_seqs: int,
                   max_q_len: int, q_heads: int, kv: KVView, scale: float, window: int, row_tiles: int, n_splits: int,
                   part_ml: Optional[torch.Tensor] = None, part_o: Optional[torch.Tensor] = None,
-                  warp_private: bool = True, sinks: Optional[torch.Tensor] = None, keep_first: int = 0) -> None:
-    """Tensor-core attention of bfloat16 q [n, q_heads*hd] over a bfloat16 cache entry (`sinks` and `keep_first` as for
-    `attention_simt`)."""
+                  warp_private: bool = True, sinks: Optional[torch.Tensor] = None, keep_first: int = 0, chunk: int = 0,
+                  softcap: float = 0.0) -> None:
+    """Tensor-core attention of bfloat16 q [n, q_heads*hd] over a bfloat16 cache entry (`sinks`, `keep_first`, `chunk` and
+    `softcap` as for `attention_simt`)."""
     require_cuda(q, out, cu_seqlens, start_pos, part_ml, part_o, sinks)
     assert sinks is None or (sinks.dtype == torch.float32 and sinks.numel() == q_heads)
     if q.dtype != torch.bfloat16 or kv.k_pool.dtype != torch.bfloat16:
@@ -1093,7 +1094,7 @@ def attention_mma(q: torch.Tensor, out: torch.Tensor, cu_seqlens: torch.Tensor, 
                                  1 if warp_private else 0, n_splits, _ptr(part_ml), _ptr(part_o), kv.k_pool.data_ptr(),
                                  kv.v_pool.data_ptr(), kv.page_table.data_ptr(), kv.entry_offset, kv.pages_per_seq,
                                  kv.page_size, int(kv.k_pool.shape[1]), gemm_status(q.device).data_ptr(), _ptr(sinks),
-                                 int(keep_first), _stream()),
+                                 int(keep_first), int(chunk), float(softcap), _stream()),
            "tensor-core attention")
     if n_splits > 1 and not in_cluster:
         _check(core().mlc_attention_combine(part_ml.data_ptr(), part_o.data_ptr(), n_tokens * q_heads, n_splits, hd,

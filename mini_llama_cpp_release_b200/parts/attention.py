@@ -165,14 +165,14 @@ class GQAttention(Part):
         sinks = getattr(self, "sinks", None)          # float32 [heads] or None: a logit per head that joins every softmax
         chunk = getattr(self, "chunk", None) or 0     # a mask of chunks instead of a window
         softcap = getattr(self, "softcap", None) or 0.0
-        if self.use_tensor_cores and not chunk and not softcap:
+        if self.use_tensor_cores:
             row_tiles, n_splits = kernels.attention_mma_plan(step.max_q_len, step.n_seqs, step.max_kv_len, self.H,
                                                              self.KV, rt.n_sms)
             if (step.max_q_len >= 16 and n_splits == 1
                     and kernels.attention_tcgen05_takes(self.hd, kv.page_size, self.H, self.KV)):
                 # prompts whose rows fill the GPU without sharing out the keys: the tcgen05 kernel
                 kernels.attention_tcgen05(q, o, step.cu_seqlens, step.start_pos, step.n_seqs, step.max_q_len, self.H, kv,
-                                          self.scale, window, sinks=sinks, keep_first=keep)
+                                          self.scale, window, sinks=sinks, keep_first=keep, chunk=chunk, softcap=softcap)
                 return
             part_ml = part_o = None
             if step.max_q_len == 1 and row_tiles == 1:
@@ -183,7 +183,8 @@ class GQAttention(Part):
                 part_ml = rt.empty(q.shape[0] * self.H * n_splits * 2, dtype=torch.float32)
                 part_o = rt.empty(q.shape[0] * self.H * n_splits * self.hd, dtype=torch.float32)
             kernels.attention_mma(q, o, step.cu_seqlens, step.start_pos, step.n_seqs, step.max_q_len, self.H, kv,
-                                  self.scale, window, row_tiles, n_splits, part_ml, part_o, sinks=sinks, keep_first=keep)
+                                  self.scale, window, row_tiles, n_splits, part_ml, part_o, sinks=sinks, keep_first=keep,
+                                  chunk=chunk, softcap=softcap)
             return
         n_splits = choose_splits(step, self.H, self.KV, rt.n_sms, tokens_per_block=max(1, 16 // min(16, self.H // self.KV)))
         part_ml = part_o = None

@@ -468,3 +468,52 @@ def test_attention_with_chunks_and_a_soft_cap_against_plain_torch():
                 i32 = lambda x: torch.tensor(x, dtype=torch.int32, device="cuda")
                 kernels.attention_simt(q, o, i32([0, q_len]), i32([start]), 1, q_len, H, kv, 0.3, chunk=chunk, softcap=cap)
                 assert helpers.rel_err(o, want[start:start + q_len]) <= 2e-5, (chunk, cap, start, q_len)
+
+
+def chunked_case(impl, lens, q_lens, H, KV, hd, chunk, cap, n_splits=1, row_tiles=4, in_cluster=False, seed=0):
+    """Sequences of `lens` cached tokens of which the last `q_lens` are the step's, through one tensor-core attention kernel
+    with a mask of chunks and a soft cap, against the plain masked softmax.  Queries are long, so single keys decide rows
+    and scores reach into the cap's bend."""
+    from test_kernels_gpu import make_paged
+    dtype = torch.bfloat16
+    g = torch.Generator().manual_seed(seed)
+    ks = [torch.randn(n, KV, hd, generator=g).to(dtype).float() for n in lens]
+    vs = [torch.randn(n, KV, hd, generator=g).to(dtype).float() for n in lens]
+    qs = [(torch.randn(n, H, hd, generator=g) * 3.0).to(dtype).float() for n in lens]
+    kv = make_paged(ks, vs, dtype, seed=seed)
+    q = torch.cat([qq[n - m:] for qq, n, m in zip(qs, lens, q_lens)]).to(dtype).cuda()
+    N = q.shape[0]
+    out = torch.empty_like(q)
+    cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32, device="cuda")
+    start = torch.tensor([n - m for n, m in zip(lens, q_lens)], dtype=torch.int32, device="cuda")
+    part_ml = torch.empty(N * H * n_splits * 2, device="cuda") if n_splits > 1 and not in_cluster else None
+    part_o = torch.empty(N * H * n_splits * hd, device="cuda") if n_splits > 1 and not in_cluster else None
+    scale = 1.0 / math.sqrt(hd)
+    args = (q.view(N, H * hd), out.view(N, H * hd), cu, start, len(lens), max(q_lens), H, kv, scale, 0)
+    if impl == "tcgen05":
+        kernels.attention_tcgen05(*args, chunk=chunk, softcap=cap)
+        torch.cuda.synchronize()
+        kernels.check_gemm_status(q.device)
+    else:
+        kernels.attention_mma(*args, row_tiles, n_splits, part_ml, part_o, chunk=chunk, softcap=cap)
+    want = torch.cat([pn.softmax_attention(qq.double(), k.double(), v.double(), scale, pn.visible(n, chunk or None), softcap=cap or None)[n - m:]
+                      for qq, k, v, n, m in zip(qs, ks, vs, lens, q_lens)]).float()
+    got = out.float().cpu().view(N, H, hd)
+    assert float((got - want).abs().max()) <= 2e-2 * float(want.abs().max()), (impl, chunk, cap, float((got - want).abs().max()))
+
+
+@pytest.mark.parametrize("hd", [64, 128, 32])
+@pytest.mark.parametrize("chunk, cap", [(50, 4.0), (64, 0.0), (130, 2.5), (1, 3.0), (0, 5.0), (300, 0.0)])
+def test_tensor_core_attention_with_chunks_and_a_soft_cap(hd, chunk, cap):
+    lens, q_lens = [330, 64, 129, 7], [330, 64, 70, 7]
+    for H, KV in ((4, 2), (3, 3)):
+        if hd in (64, 128):
+            chunked_case("tcgen05", lens, q_lens, H, KV, hd, chunk, cap, seed=hd + chunk)
+        for row_tiles in (4, 1):
+            chunked_case("mma", lens, q_lens, H, KV, hd, chunk, cap, row_tiles=row_tiles, seed=hd + chunk + 1)
+        chunked_case("mma", lens, q_lens, H, KV, hd, chunk, cap, n_splits=3, row_tiles=4, seed=hd + chunk + 2)
+        # single tokens: the decode form, keys shared out inside a cluster and through partial results
+        dec = [331, 65, 130, 200, 1, 51]
+        chunked_case("mma", dec, [1] * len(dec), H, KV, hd, chunk, cap, n_splits=1, row_tiles=1, seed=hd + chunk + 3)
+        chunked_case("mma", dec, [1] * len(dec), H, KV, hd, chunk, cap, n_splits=2, row_tiles=1, in_cluster=True, seed=hd + chunk + 4)
+        chunked_case("mma", dec, [1] * len(dec), H, KV, hd, chunk, cap, n_splits=3, row_tiles=1, seed=hd + chunk + 5)
