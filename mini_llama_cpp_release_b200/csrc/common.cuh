@@ -112,6 +112,21 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
     return t;
 }
 
+// A gated unit act(gate) · up, in float32.  KIND 0: gate · sigmoid(gate) (SiLU); 1: the tanh form of GELU, written as
+// gate / (1 + exp(-2w)), w = sqrt(2/pi)(gate + 0.044715 gate³), the same function without the sum that cancels for negative w;
+// 2: clamped, g = min(gate, limit), u = clamp(up, -limit, limit), g · sigmoid(alpha · g) · (u + 1).
+template <int KIND>
+__device__ __forceinline__ float glu_act(float gate, float up, float limit, float alpha) {
+    if constexpr (KIND == 0) return __fdividef(gate, 1.0f + __expf(-gate)) * up;
+    else if constexpr (KIND == 1) {
+        const float w = 0.7978845608028654f * (gate + 0.044715f * gate * gate * gate);
+        return __fdividef(gate, 1.0f + __expf(-2.0f * w)) * up;
+    } else {
+        const float g = fminf(gate, limit), u = fminf(fmaxf(up, -limit), limit);
+        return __fdividef(g, 1.0f + __expf(-alpha * g)) * (u + 1.0f);
+    }
+}
+
 // Where the keys and values of one cache entry live: pools of pages of `page_size`
 // tokens, [entry][page][kv_head][token in page][head_dim], and each sequence's list of
 // pages.  A negative page number marks a page that was never given or was given back.

@@ -34,6 +34,10 @@ struct RowsArgs {
     // STORE only: an activation applied to the product before it is stored (0 none, 1 silu, 2 gelu with erf, 3 gelu with
     // the tanh approximation), in float32
     int act;
+    // SILU_MUL only: which gated unit the epilogue forms from the alternating gate and up columns (0 SiLU, 1 the tanh form of
+    // GELU, 2 clamped with `glu_limit` and `glu_alpha`: see glu_act)
+    int glu_kind;
+    float glu_limit, glu_alpha;
 };
 
 // One activation over a chunk of accumulator columns.  The kind is tested once per chunk, outside the unrolled loop: with
@@ -99,10 +103,16 @@ __device__ __forceinline__ void rows_epilogue_chunk(const RowsArgs& g, const flo
             if (u < 4 || second) atomicAdd(dst + u, make_float4(v[4 * u], v[4 * u + 1], v[4 * u + 2], v[4 * u + 3]));
     } else {                                          // SILU_MUL: columns alternate gate_j, up_j
         float act[16];
+        // the kind is tested once per chunk, outside the unrolled loops
+        if (g.glu_kind == 0) {
 #pragma unroll
-        for (int u = 0; u < 16; ++u) {
-            const float gate = v[2 * u], up = v[2 * u + 1];
-            act[u] = __fdividef(gate, 1.0f + __expf(-gate)) * up;
+            for (int u = 0; u < 16; ++u) act[u] = glu_act<0>(v[2 * u], v[2 * u + 1], 0.0f, 0.0f);
+        } else if (g.glu_kind == 1) {
+#pragma unroll
+            for (int u = 0; u < 16; ++u) act[u] = glu_act<1>(v[2 * u], v[2 * u + 1], 0.0f, 0.0f);
+        } else {
+#pragma unroll
+            for (int u = 0; u < 16; ++u) act[u] = glu_act<2>(v[2 * u], v[2 * u + 1], g.glu_limit, g.glu_alpha);
         }
         const long long at = (long long)tok * (g.n_out >> 1) + (n >> 1);
         if (g.out_dtype == MLC_DTYPE_BF16) {

@@ -72,6 +72,9 @@ struct GemmArgs {
     int rope_positions;
     int q_heads, kv_heads, hd;
     PagedKV cache;
+    // SILU_MUL only: which gated unit the epilogue forms (0 SiLU, 1 the tanh form of GELU, 2 clamped: see glu_act)
+    int glu_kind;
+    float glu_limit, glu_alpha;
 };
 
 template <int BN, int EPI> struct GemmShape {
@@ -430,7 +433,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                             const float recv = __shfl_xor_sync(0xffffffffu, send, 1);
                             const float gate = (lane & 1) ? recv : v[jj];
                             const float up = (lane & 1) ? v[jj + 1] : recv;
-                            const float act = __fdividef(gate, 1.0f + __expf(-gate)) * up;
+                            const float act = g.glu_kind == 0 ? glu_act<0>(gate, up, 0.0f, 0.0f)
+                                              : g.glu_kind == 1 ? glu_act<1>(gate, up, 0.0f, 0.0f)
+                                                                : glu_act<2>(gate, up, g.glu_limit, g.glu_alpha);
                             stage[(cl + jj + (lane & 1)) * 16 + (lane >> 1)] = __float2bfloat16_rn(act);
                         }
                     } else {
@@ -440,7 +445,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                             const int tok = n0 + c0 + jj;
                             if ((lane & 1) == 0 && row < g.n_out && tok < g.n_tok) {
                                 const float gate = v[jj], up = other;
-                                const float act = gate * (1.0f / (1.0f + expf(-gate))) * up;
+                                const float act = g.glu_kind == 0 ? gate * (1.0f / (1.0f + expf(-gate))) * up
+                                                  : g.glu_kind == 1 ? glu_act<1>(gate, up, 0.0f, 0.0f)
+                                                                    : glu_act<2>(gate, up, g.glu_limit, g.glu_alpha);
                                 const long long idx = (long long)tok * half_out + (row >> 1);
                                 if (g.out_dtype == MLC_DTYPE_F32) store_out<float>(g.out, idx, act);
                                 else store_out<bf16>(g.out, idx, act);
@@ -672,7 +679,7 @@ extern "C" int mlc_gemm_tcgen05(const void* x, const void* w, void* out, int out
                                 int n_sms, const float* bias, const int* positions, const int* tok_seq,
                                 const void* rope_table, int rope_positions, int q_heads, int kv_heads, int hd,
                                 void* k_pool, void* v_pool, const int* page_table, long long entry_offset,
-                                int pages_per_seq, int page_size, void* stream) {
+                                int pages_per_seq, int page_size, int glu_kind, float glu_limit, float glu_alpha, void* stream) {
     if (n_tok <= 0 || n_out <= 0) return 0;
     if (K <= 0 || (K & 7) || (((uintptr_t)x | (uintptr_t)w) & 15)) return MLC_ERR_BAD_SIZE;
     if (out_dtype != MLC_DTYPE_F32 && out_dtype != MLC_DTYPE_BF16) return MLC_ERR_BAD_DTYPE;
@@ -683,6 +690,10 @@ extern "C" int mlc_gemm_tcgen05(const void* x, const void* w, void* out, int out
     if (epilogue == EPI_ADD && out_dtype != MLC_DTYPE_F32) return MLC_ERR_BAD_DTYPE;
     if (n_sms < 1) return MLC_ERR_BAD_SIZE;
     GemmArgs g{};
+    if (glu_kind < 0 || glu_kind > 2 || (glu_kind == 2 && !(glu_limit > 0.0f))) return MLC_ERR_UNSUPPORTED;
+    g.glu_kind = glu_kind;
+    g.glu_limit = glu_limit;
+    g.glu_alpha = glu_alpha;
     g.out = out;
     g.out_dtype = out_dtype;
     g.n_out = n_out;

@@ -285,7 +285,7 @@ using namespace mlc;
 // out over that many pairs per tile, which then add atomically.  status: one int on the device, 0 before the call; a
 // bounded wait that ran out leaves 41, 42 or 43 there.  n_sms: blocks to launch at most (an even number is used).
 extern "C" int mlc_gemm_tcgen05_pair(const void* x, const void* w, void* out, int out_dtype, int n_tok, int n_out, int K,
-                                     int block_rows, int n_splits, int epilogue, int* status, int n_sms, void* stream) {
+                                     int block_rows, int n_splits, int epilogue, int* status, int n_sms, int glu_kind, float glu_limit, float glu_alpha, void* stream) {
     if (n_tok <= 0 || n_out <= 0) return 0;
     if (K <= 0 || (K & 7) || (n_out & 15) || (((uintptr_t)x | (uintptr_t)w | (uintptr_t)out) & 15)) return MLC_ERR_BAD_SIZE;
     if (out_dtype != MLC_DTYPE_F32 && out_dtype != MLC_DTYPE_BF16) return MLC_ERR_BAD_DTYPE;
@@ -293,6 +293,10 @@ extern "C" int mlc_gemm_tcgen05_pair(const void* x, const void* w, void* out, in
     if (epilogue == R_EPI_ADD && out_dtype != MLC_DTYPE_F32) return MLC_ERR_BAD_DTYPE;
     if (n_splits < 1 || (n_splits > 1 && epilogue != R_EPI_ADD)) return MLC_ERR_BAD_SIZE;
     RowsArgs g{};
+    if (glu_kind < 0 || glu_kind > 2 || (glu_kind == 2 && !(glu_limit > 0.0f))) return MLC_ERR_UNSUPPORTED;
+    g.glu_kind = glu_kind;
+    g.glu_limit = glu_limit;
+    g.glu_alpha = glu_alpha;
     g.out = out;
     g.out_dtype = out_dtype;
     g.n_out = n_out;

@@ -310,7 +310,7 @@ extern "C" int mlc_gemm_tcgen05_rows(const void* x, const void* w, void* out, in
                                      int block_rows, int n_splits, int epilogue, int* status, int n_sms, const float* bias,
                                      const int* positions, const int* tok_seq, const void* rope_table, int rope_positions,
                                      int q_heads, int kv_heads, int hd, void* k_pool, void* v_pool, const int* page_table,
-                                     long long entry_offset, int pages_per_seq, int page_size, void* stream) {
+                                     long long entry_offset, int pages_per_seq, int page_size, int glu_kind, float glu_limit, float glu_alpha, void* stream) {
     if (n_tok <= 0 || n_out <= 0) return 0;
     if (K <= 0 || (K & 7) || (n_out & 15) || (((uintptr_t)x | (uintptr_t)w | (uintptr_t)out) & 15)) return MLC_ERR_BAD_SIZE;
     if (out_dtype != MLC_DTYPE_F32 && out_dtype != MLC_DTYPE_BF16) return MLC_ERR_BAD_DTYPE;
@@ -318,6 +318,10 @@ extern "C" int mlc_gemm_tcgen05_rows(const void* x, const void* w, void* out, in
     if (epilogue == R_EPI_ADD && out_dtype != MLC_DTYPE_F32) return MLC_ERR_BAD_DTYPE;
     if (n_splits < 1 || (n_splits > 1 && epilogue != R_EPI_ADD)) return MLC_ERR_BAD_SIZE;
     RowsArgs g{};
+    if (glu_kind < 0 || glu_kind > 2 || (glu_kind == 2 && !(glu_limit > 0.0f))) return MLC_ERR_UNSUPPORTED;
+    g.glu_kind = glu_kind;
+    g.glu_limit = glu_limit;
+    g.glu_alpha = glu_alpha;
     g.out = out;
     g.out_dtype = out_dtype;
     g.n_out = n_out;
@@ -364,13 +368,17 @@ extern "C" int mlc_gemm_tcgen05_rows(const void* x, const void* w, void* out, in
 // approximation applied to the product before it is stored).  Status codes as above.
 extern "C" int mlc_gemm_tcgen05_rows_grouped(const void* x, const void* w, void* out, int out_dtype, int n_rows, int n_out, int K,
                                              int block_rows, int epilogue, int* status, int n_sms, const int* tile_group,
-                                             int n_groups, void* stream) {
+                                             int n_groups, int glu_kind, float glu_limit, float glu_alpha, void* stream) {
     if (n_rows <= 0 || n_out <= 0) return 0;
     if (K <= 0 || (K & 7) || (n_out & 15) || (n_rows % R_BM) || (((uintptr_t)x | (uintptr_t)w | (uintptr_t)out) & 15)) return MLC_ERR_BAD_SIZE;
     if (out_dtype != MLC_DTYPE_F32 && out_dtype != MLC_DTYPE_BF16) return MLC_ERR_BAD_DTYPE;
     if (status == nullptr || n_sms < 1 || tile_group == nullptr || n_groups < 1) return MLC_ERR_BAD_SIZE;
     if (epilogue != R_EPI_STORE && epilogue != R_EPI_SILU_MUL && (epilogue < 4 || epilogue > 6)) return MLC_ERR_UNSUPPORTED;
     RowsArgs g{};
+    if (glu_kind < 0 || glu_kind > 2 || (glu_kind == 2 && !(glu_limit > 0.0f))) return MLC_ERR_UNSUPPORTED;
+    g.glu_kind = glu_kind;
+    g.glu_limit = glu_limit;
+    g.glu_alpha = glu_alpha;
     if (epilogue >= 4) {
         g.act = epilogue - 3;
         epilogue = R_EPI_STORE;

@@ -128,10 +128,10 @@ def core() -> ctypes.CDLL:
             "mlc_head_project": [P, I, LL, LL, P, I, LL, LL, LL, P, I, LL, LL, I, I, I, I, P],
             "mlc_linear_simt": [P, I, P, I, P, I, I, I, I, P, LL, I, P],
             "mlc_attention_combine": [P, P, LL, I, I, P, I, P, I, P],
-            "mlc_gemm_tcgen05": [P, P, P, I, I, I, I, I, I, I, P, P, I, P, P, P, P, I, I, I, I, P, P, P, LL, I, I, P],
-            "mlc_gemm_tcgen05_rows": [P, P, P, I, I, I, I, I, I, I, P, I, P, P, P, P, I, I, I, I, P, P, P, LL, I, I, P],
-            "mlc_gemm_tcgen05_pair": [P, P, P, I, I, I, I, I, I, I, P, I, P],
-            "mlc_gemm_tcgen05_rows_grouped": [P, P, P, I, I, I, I, I, I, P, I, P, I, P],
+            "mlc_gemm_tcgen05": [P, P, P, I, I, I, I, I, I, I, P, P, I, P, P, P, P, I, I, I, I, P, P, P, LL, I, I, I, F, F, P],
+            "mlc_gemm_tcgen05_rows": [P, P, P, I, I, I, I, I, I, I, P, I, P, P, P, P, I, I, I, I, P, P, P, LL, I, I, I, F, F, P],
+            "mlc_gemm_tcgen05_pair": [P, P, P, I, I, I, I, I, I, I, P, I, I, F, F, P],
+            "mlc_gemm_tcgen05_rows_grouped": [P, P, P, I, I, I, I, I, I, P, I, P, I, I, F, F, P],
             "mlc_copy_async": [P, P, LL, I, P],
             "mlc_argmax": [P, I, I, P, P],
             "mlc_argmax_split": [P, I, I, P, P, P, P, P],
@@ -1190,8 +1190,21 @@ def gemm_rows_block(n_tok: int, n_out: int, n_sms: int) -> int:
     return best
 
 
+
+def _glu_args(glu) -> tuple:
+    """(kind, limit, alpha) of the gated unit an EPI_SILU_MUL epilogue forms: None or "silu"; "gelu_tanh"; ("clamped", limit, alpha)."""
+    if glu is None or glu == "silu":
+        return (0, 0.0, 1.0)
+    if glu == "gelu_tanh":
+        return (1, 0.0, 1.0)
+    kind, limit, alpha = glu
+    if kind != "clamped":
+        raise KernelError(f"unknown gated unit {glu!r}")
+    return (2, float(limit), float(alpha))
+
+
 def gemm_tcgen05_pair(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = 0, block_rows: int = 256,
-                      n_splits: int = 1, n_sms: int = 0) -> None:
+                      n_splits: int = 1, n_sms: int = 0, glu=None) -> None:
     """The tcgen05 product for prompts with a pair of SMs on every tile of 256 tokens x `block_rows` rows of w
     (csrc/gemm_tcgen05_pair.cu): epilogues EPI_STORE, EPI_SILU_MUL, EPI_ADD as `gemm_tcgen05_rows`."""
     require_cuda(x, w, out)
@@ -1214,7 +1227,7 @@ def gemm_tcgen05_pair(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilo
         assert out.numel() == n_tok * n_out and (epilogue != EPI_ADD or out.dtype == torch.float32)
     status = gemm_status(x.device)
     _check(core().mlc_gemm_tcgen05_pair(x.data_ptr(), w.data_ptr(), out.data_ptr(), dtype_code(out.dtype), n_tok, n_out, K,
-                                        block_rows, n_splits, epilogue, status.data_ptr(), n_sms, _stream()),
+                                        block_rows, n_splits, epilogue, status.data_ptr(), n_sms, *_glu_args(glu), _stream()),
            "tcgen05 matrix product (paired prompt form)")
 
 
@@ -1228,8 +1241,9 @@ def gemm_pair_takes(n_tok: int, n_out: int, k: int, n_sms: int) -> bool:
     return ((n_tok + 255) // 256) * ((n_out + 255) // 256) >= n_sms
 
 
-def gemm_prompt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, n_sms: int = 0) -> None:
-    """A prompt product with epilogue EPI_STORE, EPI_SILU_MUL or EPI_ADD on whichever form suits its sizes."""
+def gemm_prompt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, n_sms: int = 0, glu=None) -> None:
+    """A prompt product with epilogue EPI_STORE, EPI_SILU_MUL or EPI_ADD on whichever form suits its sizes.  `glu`: the gated
+    unit EPI_SILU_MUL forms (default SiLU; "gelu_tanh"; ("clamped", limit, alpha))."""
     if n_sms <= 0:
         n_sms = _sm_count(x.device)
     if epilogue == EPI_ADD:
@@ -1239,9 +1253,9 @@ def gemm_prompt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: i
         else:
             gemm_tcgen05_rows(x, w, out, epilogue, block_rows, n_splits, n_sms=n_sms)
     elif gemm_pair_takes(x.shape[0], w.shape[0], x.shape[1], n_sms):
-        gemm_tcgen05_pair(x, w, out, epilogue, 256, 1, n_sms)
+        gemm_tcgen05_pair(x, w, out, epilogue, 256, 1, n_sms, glu=glu)
     else:
-        gemm_tcgen05_rows(x, w, out, epilogue, n_sms=n_sms)
+        gemm_tcgen05_rows(x, w, out, epilogue, n_sms=n_sms, glu=glu)
 
 
 # What an adding prompt product costs in microseconds, by form: a launch, per K step a part that grows with the tile's
@@ -1298,7 +1312,7 @@ def gemm_tcgen05_rows(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilo
                       block_rows: Optional[int] = None, n_splits: Optional[int] = None, bias: Optional[torch.Tensor] = None,
                       positions: Optional[torch.Tensor] = None, tok_seq: Optional[torch.Tensor] = None,
                       rope: Optional[torch.Tensor] = None, q_heads: int = 0, kv_heads: int = 0, head_dim: int = 0,
-                      kv: Optional[KVView] = None, n_sms: int = 0) -> None:
+                      kv: Optional[KVView] = None, n_sms: int = 0, glu=None) -> None:
     """The tcgen05 product for prompts (csrc/gemm_tcgen05_rows.cu): bfloat16 x [n, K] times bfloat16 w [rows, K]
     transposed, tiles of 128 tokens x `block_rows` (128 to 256 in steps of 32) rows of w, the same epilogues as `gemm_tcgen05`;
     EPI_ADD adds into `out` (float32 [n, rows]) with 16-byte atomic adds, the K range shared out over `n_splits` blocks per
@@ -1339,14 +1353,14 @@ def gemm_tcgen05_rows(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilo
     _check(core().mlc_gemm_tcgen05_rows(x.data_ptr(), w.data_ptr(), out.data_ptr(), dtype_code(out.dtype), n_tok, n_out, K,
                                         block_rows, n_splits, epilogue, status.data_ptr(), n_sms, _ptr(bias), _ptr(positions),
                                         _ptr(tok_seq), _ptr(rope), rope.shape[0] if rope is not None else 0, q_heads,
-                                        kv_heads, head_dim, *cache, _stream()), "tcgen05 matrix product (prompt form)")
+                                        kv_heads, head_dim, *cache, *_glu_args(glu), _stream()), "tcgen05 matrix product (prompt form)")
 
 
 GROUPED_TILE = 128           # rows per tile of the grouped tcgen05 product: a group's run of rows starts on a multiple of it
 
 
 def gemm_tcgen05_grouped(x: torch.Tensor, w: torch.Tensor, tile_group: torch.Tensor, out: torch.Tensor, epilogue: int = 0,
-                         n_sms: int = 0) -> None:
+                         n_sms: int = 0, glu=None) -> None:
     """The prompt form of the tcgen05 product with a matrix per group of rows (csrc/gemm_tcgen05_rows.cu): bfloat16 x
     [rows, K], rows a multiple of 128; bfloat16 w [groups, n_out, K]; tile_group int32 [rows / 128] gives every tile of
     128 rows its group (negative: skipped).  EPI_STORE: out [rows, n_out]; EPI_SILU_MUL (w's rows alternate gate and
@@ -1369,7 +1383,7 @@ def gemm_tcgen05_grouped(x: torch.Tensor, w: torch.Tensor, tile_group: torch.Ten
     status = gemm_status(x.device)
     _check(core().mlc_gemm_tcgen05_rows_grouped(x.data_ptr(), w.data_ptr(), out.data_ptr(), dtype_code(out.dtype), rows, n_out, K,
                                                 block_rows, epilogue, status.data_ptr(), n_sms, tile_group.data_ptr(), groups,
-                                                _stream()), "grouped tcgen05 matrix product")
+                                                *_glu_args(glu), _stream()), "grouped tcgen05 matrix product")
 
 
 @functools.lru_cache(maxsize=None)
@@ -1402,7 +1416,7 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: 
                  block_tokens: Optional[int] = None, bias: Optional[torch.Tensor] = None,
                  positions: Optional[torch.Tensor] = None, tok_seq: Optional[torch.Tensor] = None,
                  rope: Optional[torch.Tensor] = None, q_heads: int = 0, kv_heads: int = 0, head_dim: int = 0,
-                 kv: Optional[KVView] = None, n_sms: int = 0) -> None:
+                 kv: Optional[KVView] = None, n_sms: int = 0, glu=None) -> None:
     """bfloat16 x [n, K] times bfloat16 w [rows, K] transposed on the tcgen05 tensor cores, with
     the epilogue done before anything is stored (see csrc/gemm_tcgen05.cu).  Epilogue EPI_ADD adds the
     product into `out` (float32 [n, rows]) with atomic adds.  `n_sms` bounds the number of (persistent) blocks."""
@@ -1441,4 +1455,4 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: 
                                    block_tokens, n_splits, epilogue, status.data_ptr(), None, n_sms,
                                    _ptr(bias), _ptr(positions),
                                    _ptr(tok_seq), _ptr(rope), rope.shape[0] if rope is not None else 0, q_heads,
-                                   kv_heads, head_dim, *cache, _stream()), "tcgen05 matrix product")
+                                   kv_heads, head_dim, *cache, *_glu_args(glu), _stream()), "tcgen05 matrix product")

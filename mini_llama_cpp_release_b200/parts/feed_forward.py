@@ -62,12 +62,12 @@ class SwiGLU(Part):
     def forward(self, h: torch.Tensor, step=None, residual=None):
         rt = self.runtime
         a = rt.empty(h.shape[0], self.inter)
-        if self.activation != "silu":
-            kernels.glu(self.gate_up(h, rt.dtype), a, self.activation, interleaved=self.fused)
-        elif self.fused and kernels.gemm_rows_takes(h.shape[0], 2 * self.inter, self.hidden):
-            kernels.gemm_prompt(h, self.gate_up.weight, a, kernels.bindings.EPI_SILU_MUL, n_sms=rt.n_sms)    # prompts
+        if self.fused and kernels.gemm_rows_takes(h.shape[0], 2 * self.inter, self.hidden):
+            kernels.gemm_prompt(h, self.gate_up.weight, a, kernels.bindings.EPI_SILU_MUL, n_sms=rt.n_sms, glu=self.activation)    # prompts
         elif self.fused:
-            kernels.gemm_tcgen05(h, self.gate_up.weight, a, kernels.bindings.EPI_SILU_MUL, n_sms=rt.n_sms)
+            kernels.gemm_tcgen05(h, self.gate_up.weight, a, kernels.bindings.EPI_SILU_MUL, n_sms=rt.n_sms, glu=self.activation)
+        elif self.activation != "silu":
+            kernels.glu(self.gate_up(h, rt.dtype), a, self.activation, interleaved=self.fused)
         else:
             kernels.silu_mul(self.gate_up(h, rt.dtype), a, interleaved=self.fused)
         if residual is not None and self.down.can_add_into_stream(h.shape[0]):
@@ -183,8 +183,8 @@ class MixtureOfExperts(Part):
         # rows.  Otherwise float32 multiply-adds on [gate; up] with tiles of 64 rows.
         self.fused = (runtime.dtype == torch.bfloat16 and self.down.dtype == torch.bfloat16 and ups[0].dtype == torch.bfloat16
                       and self.hidden % 16 == 0 and self.inter % (8 if self.gated else 16) == 0)
-        # whether the gated product's epilogue applies the activation, or a kernel of its own behind a plain store
-        self.fused_act = self.activation == "silu"
+        # the gated unit the grouped product's epilogue forms
+        self.glu = ("clamped", self.limit, self.act_alpha) if self.activation == "clamped" else self.activation
         if not self.gated:
             self.gate_up = torch.stack(ups).contiguous()
         elif self.fused:
@@ -246,12 +246,9 @@ class MixtureOfExperts(Part):
         if self.fused:
             hs = rt.empty(rows, self.hidden)
             kernels.moe_gather(h, src_tok, hs, *on_input)            # the sorted rows, dense, as the product's TMA loads want them
-            if self.gated and not self.fused_act:
-                gu = rt.empty(rows, 2 * self.inter)
-                kernels.gemm_tcgen05_grouped(hs, self.gate_up, tile_expert, gu, kernels.bindings.EPI_STORE, n_sms=rt.n_sms)
-                kernels.glu(gu, act, self.activation, interleaved=True, limit=self.limit, alpha=self.act_alpha)
-            elif self.gated:
-                kernels.gemm_tcgen05_grouped(hs, self.gate_up, tile_expert, act, kernels.bindings.EPI_SILU_MUL, n_sms=rt.n_sms)
+            if self.gated:
+                kernels.gemm_tcgen05_grouped(hs, self.gate_up, tile_expert, act, kernels.bindings.EPI_SILU_MUL, n_sms=rt.n_sms,
+                                             glu=self.glu)
             else:
                 kernels.gemm_tcgen05_grouped(hs, self.gate_up, tile_expert, act, kernels.bindings.EPI_ACT[self.activation], n_sms=rt.n_sms)
             kernels.gemm_tcgen05_grouped(act, self.down, tile_expert, y, kernels.bindings.EPI_STORE, n_sms=rt.n_sms)

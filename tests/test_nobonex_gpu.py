@@ -517,3 +517,48 @@ def test_tensor_core_attention_with_chunks_and_a_soft_cap(hd, chunk, cap):
         chunked_case("mma", dec, [1] * len(dec), H, KV, hd, chunk, cap, n_splits=1, row_tiles=1, seed=hd + chunk + 3)
         chunked_case("mma", dec, [1] * len(dec), H, KV, hd, chunk, cap, n_splits=2, row_tiles=1, in_cluster=True, seed=hd + chunk + 4)
         chunked_case("mma", dec, [1] * len(dec), H, KV, hd, chunk, cap, n_splits=3, row_tiles=1, seed=hd + chunk + 5)
+
+
+@pytest.mark.parametrize("glu", ["gelu_tanh", ("clamped", 1.5, 1.702), "silu"])
+def test_gated_units_in_the_epilogues_of_the_tensor_core_products(glu):
+    """gate and up rows alternate in w; the product's epilogue forms the gated unit from the float32 accumulators: the
+    few-token form, the prompt form on one SM and on a pair of SMs, and the grouped form."""
+    g = torch.Generator().manual_seed(17)
+    K, inter = 192, 256
+    w = (torch.randn(2 * inter, K, generator=g) * 0.2).bfloat16().cuda()
+    gate_w, up_w = w[0::2].double(), w[1::2].double()
+
+    def want_of(x, gw=gate_w, uw=up_w):
+        gate, up = x.double() @ gw.t(), x.double() @ uw.t()
+        if glu == "silu":
+            return pn.silu(gate) * up
+        if glu == "gelu_tanh":
+            return pn.gelu_tanh(gate) * up
+        gc, uc = gate.clamp(max=glu[1]), up.clamp(-glu[1], glu[1])
+        return gc * torch.sigmoid(glu[2] * gc) * (uc + 1.0)
+    for n, form in ((5, "few"), (40, "few"), (300, "rows"), (512, "pair")):
+        x = torch.randn(n, K, generator=g).bfloat16().cuda()
+        out = torch.empty(n, inter, dtype=torch.bfloat16, device="cuda")
+        if form == "few":
+            kernels.gemm_tcgen05(x, w, out, kernels.bindings.EPI_SILU_MUL, glu=glu)
+        elif form == "rows":
+            kernels.gemm_tcgen05_rows(x, w, out, kernels.bindings.EPI_SILU_MUL, glu=glu)
+        else:
+            kernels.gemm_tcgen05_pair(x, w, out, kernels.bindings.EPI_SILU_MUL, glu=glu)
+        torch.cuda.synchronize()
+        kernels.check_gemm_status(x.device)
+        assert helpers.rel_err(out, want_of(x)) <= 1.5e-2, (form, n)
+    # grouped: three matrices, tiles of 128 rows each with a group of its own, one tile skipped
+    w3 = (torch.randn(3, 2 * inter, K, generator=g) * 0.2).bfloat16().cuda()
+    x = torch.randn(4 * 128, K, generator=g).bfloat16().cuda()
+    tiles = torch.tensor([2, 0, -1, 1], dtype=torch.int32, device="cuda")
+    out = torch.zeros(4 * 128, inter, dtype=torch.bfloat16, device="cuda")
+    kernels.gemm_tcgen05_grouped(x, w3, tiles, out, kernels.bindings.EPI_SILU_MUL, glu=glu)
+    torch.cuda.synchronize()
+    kernels.check_gemm_status(x.device)
+    for t, e in enumerate(tiles.tolist()):
+        rows = slice(128 * t, 128 * (t + 1))
+        if e < 0:
+            assert float(out[rows].abs().max()) == 0.0
+        else:
+            assert helpers.rel_err(out[rows], want_of(x[rows], w3[e, 0::2].double(), w3[e, 1::2].double())) <= 1.5e-2, t
