@@ -5,6 +5,7 @@
     python bench.py --impl reference      # the reference project's own GPU path on the same work
     python bench.py --compare mepolix-w896 [--layers 6]   # the Mepolix (or, kebesun-w896, the Kebesun) design beside Qwen2 at equal sizes (a line of its own)
     python bench.py --compare lonulix-w896 [--layers 6]   # the Lonulix design beside Kebesun layers of the same mixers and sizes
+    python bench.py --compare nobonex-w896 [--layers 6]   # the Nobonex design beside the Kebesun preset of the same sizes
 
 A "step" is one decode step of the whole batch.  The default run (`--config qwen2-0.5b`) has the layer sizes of a
 Qwen2-0.5B (24 layers, width 896, 14 query heads on 2 kv heads of size 64, feed-forward 4864, vocabulary 151936,
@@ -48,7 +49,9 @@ CONFIGS = {
 COMPARE = {"mepolix-w896": "qwen2-0.5b", "mepolix-w1536": "qwen2-1.5b", "mepolix-w3584": "qwen2-7b",
            "kebesun-w896": "qwen2-0.5b", "kebesun-w1536": "qwen2-1.5b", "kebesun-w3584": "qwen2-7b",
            # a Lonulix preset → the Kebesun layers of the same mixers, sizes and order (its closest design)
-           "lonulix-w896": "kebesun-lg-w896", "lonulix-w1536": "kebesun-lg-w1536", "lonulix-w3584": "kebesun-lg-w3584"}
+           "lonulix-w896": "kebesun-lg-w896", "lonulix-w1536": "kebesun-lg-w1536", "lonulix-w3584": "kebesun-lg-w3584",
+           # a Nobonex preset → the Kebesun preset of the same width, attention shape, feed-forward and experts (its closest design)
+           "nobonex-w896": "kebesun-w896", "nobonex-w1536": "kebesun-w1536", "nobonex-w3584": "kebesun-w3584"}
 REF_DIR = os.path.join(ROOT, "baseline", "_ref")
 REF_SOURCE = os.environ.get("MLC_REFERENCE_SOURCE", "/root/reference")     # where the reference's checkout lies, if baseline/_ref is empty
 REF_PREFILL_TOKENS = 32
@@ -194,7 +197,7 @@ def main() -> int:
                     help="run one part only and print a short line (for profiling a small case)")
     ap.add_argument("--prompt-len", type=int, default=None, help="prompt length of the --only runs")
     ap.add_argument("--compare", default=None, choices=sorted(COMPARE),
-                    help="instead of the benchmark line: prompt and decode throughput of a Mepolix, Kebesun or Lonulix preset beside the "
+                    help="instead of the benchmark line: prompt and decode throughput of a Mepolix, Kebesun, Lonulix or Nobonex preset beside the "
                          "preset of its closest design at the same width, head shape and feed-forward, at --layers layers each "
                          "(default 6)")
     args = ap.parse_args()

@@ -86,6 +86,32 @@ def _lonulix(width: int, ff: int, heads: int, head: int, n_layers: int, vocab: i
     return dict(top, layers=[{"type": t, "mixer": dict(m), "mlp": dict(f)} for t, m, f in (cycle[i % 4] for i in range(n_layers))])
 
 
+def _nobonex(width: int, ff: int, heads: int, kv_heads: int, head: int, n_layers: int, vocab: int) -> Dict[str, Any]:
+    """Nobonex layers of real width in a cycle of six: gated chunked attention with the dense feed-forward, the same attention
+    on the keys and values of the layer before it with experts, a state-space layer with experts, attention over convolved
+    keys with experts, gated chunked attention with the dense feed-forward, a state-space layer with experts.  The attention's
+    shape (heads, kv heads, head size), the width, the dense feed-forward and the experts (eight of half the dense size, two
+    chosen) are the Kebesun preset's of the same width, which it is timed beside; chunks of 1,024 keys stand where that
+    preset has windows of 1,024; the state-space layers are twice the width inside, in heads of 64 with a state of 128."""
+    rot = {"dims": head // 2, "base": 1000000.0, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}
+    gated = {"heads": heads, "kv_heads": kv_heads, "dim": head, "vdim": head, "scale": head ** -0.5, "softcap": 30.0, "rot": rot,
+             "mask": {"size": 1024}}
+    conv = {"heads": heads, "kv_heads": kv_heads, "dim": head, "vdim": head, "conv": 3, "scale": head ** -0.5,
+            "rot": {"dims": head // 2, "base": 10000.0}}
+    m_heads = 2 * width // 64
+    groups = next(g for g in (8, 4, 2, 1) if m_heads % g == 0)
+    ssm = {"heads": m_heads, "vdim": 64, "state": 128, "groups": groups, "conv": 4, "norm_groups": groups}
+    dense = {"kind": "dense", "ff": ff}
+    moe = {"kind": "moe", "expert": {"ff": ff // 2, "limit": 7.0}, "router": {"experts": 8, "top": 2}}
+    layers = []
+    for i in range(n_layers):
+        t, m, f = [("attention_2", gated, dense), ("attention_2", dict(gated, kv_from=i - 1), moe), ("mamba2", ssm, moe),
+                   ("attention", conv, moe), ("attention_2", gated, dense), ("mamba2", ssm, moe)][i % 6]
+        layers.append({"type": t, "mixer": dict(m), "mlp": dict(f)})
+    return {"architecture": "Nobonex", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "residual_mult": 0.5,
+            "embedding": {"scale": 4.0}, "layers": layers}
+
+
 PRESETS: Dict[str, Dict[str, Any]] = {
     "tiny-a": dict(_QWEN2, hidden_size=64, intermediate_size=176, num_hidden_layers=2, num_attention_heads=4,
                    num_key_value_heads=2, head_dim=16, vocab_size=512, max_position_embeddings=256, rope_theta=10000.0,
@@ -117,6 +143,10 @@ PRESETS: Dict[str, Dict[str, Any]] = {
     "kebesun-lg-w896": _lonulix(896, 4864, 14, 64, 24, 151936, design="Kebesun"),
     "kebesun-lg-w1536": _lonulix(1536, 8960, 12, 128, 24, 151936, design="Kebesun"),
     "kebesun-lg-w3584": _lonulix(3584, 18944, 28, 128, 24, 152064, design="Kebesun"),
+    # the Nobonex design at the same widths (see `_nobonex`), timed beside the Kebesun presets above
+    "nobonex-w896": _nobonex(896, 4864, 14, 2, 64, 24, 151936),
+    "nobonex-w1536": _nobonex(1536, 8960, 12, 2, 128, 24, 151936),
+    "nobonex-w3584": _nobonex(3584, 18944, 28, 4, 128, 24, 152064),
 }
 
 FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0)

@@ -110,7 +110,8 @@ def test_model_comes_from_a_folder_a_file_or_a_random_configuration(tmp_path, mo
     # the presets are the configurations the measurements are quoted on
     assert sorted(measure.PRESETS) == ["kebesun-lg-w1536", "kebesun-lg-w3584", "kebesun-lg-w896", "kebesun-w1536", "kebesun-w3584",
                                        "kebesun-w896", "lonulix-w1536", "lonulix-w3584", "lonulix-w896", "mepolix-w1536",
-                                       "mepolix-w3584", "mepolix-w896", "qwen2-0.5b", "qwen2-1.5b", "qwen2-7b", "tiny-a", "tiny-b"]
+                                       "mepolix-w3584", "mepolix-w896", "nobonex-w1536", "nobonex-w3584", "nobonex-w896", "qwen2-0.5b",
+                                       "qwen2-1.5b", "qwen2-7b", "tiny-a", "tiny-b"]
     for raw in measure.PRESETS.values():
         helpers.ml.ModelConfig.from_dict(raw)
     # the engine's sizes
