@@ -38,48 +38,92 @@ struct TanhNormArgs {
     long long total;            // n · d
 };
 
-__device__ __forceinline__ float tanh_norm_one(float v, float alpha, float gain, float bias) { return tanhf(alpha * v) * gain + bias; }
+// tanh for the norm.  EXACT: the library's tanhf (the float32 engine).  Otherwise 1 - 2 / (1 + e^2v) with the fast exponential
+// and division, whose absolute error stays at float32's rounding of one (1e-7): for an engine whose products take 16-bit
+// operands, where the norm's output is rounded to 16 bits and the stream it is added to is of the order of one.
+template <bool EXACT>
+__device__ __forceinline__ float tanh_of(float v) {
+    if constexpr (EXACT) return tanhf(v);
+    else return 1.0f - __fdividef(2.0f, 1.0f + __expf(2.0f * v));
+}
 
-template <typename TOut, int VEC>
+template <bool EXACT>
+__device__ __forceinline__ float tanh_norm_one(float v, float alpha, float gain, float bias) { return fmaf(tanh_of<EXACT>(alpha * v), gain, bias); }
+
+__device__ __forceinline__ void load_vec(const float* p, float (&v)[4]) {
+    const float4 t = *reinterpret_cast<const float4*>(p);
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+}
+__device__ __forceinline__ void load_vec(const float* p, float (&v)[1]) { v[0] = *p; }
+__device__ __forceinline__ void store_vec(float* p, const float (&v)[4]) { *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]); }
+__device__ __forceinline__ void store_vec(float* p, const float (&v)[1]) { *p = v[0]; }
+__device__ __forceinline__ void store_vec(bf16* p, const float (&v)[4]) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
+    *reinterpret_cast<uint2*>(p) = make_uint2(*reinterpret_cast<const unsigned*>(&lo), *reinterpret_cast<const unsigned*>(&hi));
+}
+__device__ __forceinline__ void store_vec(bf16* p, const float (&v)[1]) { *p = __float2bfloat16_rn(v[0]); }
+
+// VEC entries a thread (4: 16-byte accesses, for rows whose length is a multiple of four; 1: steps of few rows, where more
+// threads with one entry each have all their loads in flight at once).  A branch's slices are added in the order of the slices.
+template <typename TOut, int VEC, bool EXACT>
 __global__ void __launch_bounds__(256)
 tanh_norm_kernel(TanhNormArgs a, TOut* __restrict__ out) {
     grid_launch_dependents();
-    grid_dependency_wait();
     const long long idx = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * VEC;
     if (idx >= a.total) return;
     const long long t = idx / a.d;
     const int c = (int)(idx - t * a.d);
+    // the norms' own numbers depend on no kernel before this one
+    float bg[VEC], bb[VEC], ng[VEC], nb[VEC];
+    if (a.b_gain != nullptr) { load_vec(a.b_gain + c, bg); load_vec(a.b_bias + c, bb); }
+    if (a.n_gain != nullptr) { load_vec(a.n_gain + c, ng); load_vec(a.n_bias + c, nb); }
+    grid_dependency_wait();
     float xv[VEC];
-#pragma unroll
-    for (int k = 0; k < VEC; ++k) xv[k] = a.x[idx + k];
+    load_vec(a.x + idx, xv);
     const bool has_branch = a.y != nullptr || a.rows != nullptr;
     if (has_branch) {
         float br[VEC];
 #pragma unroll
         for (int k = 0; k < VEC; ++k) br[k] = 0.0f;
         if (a.y != nullptr) {
-            for (int s = 0; s < a.n_slices; ++s)
+            int s = 0;
+            for (; s + 4 <= a.n_slices; s += 4) {                    // four slices' loads in flight together, added in order
+                float p0[VEC], p1[VEC], p2[VEC], p3[VEC];
+                load_vec(a.y + (long long)s * a.slice_stride + idx, p0);
+                load_vec(a.y + (long long)(s + 1) * a.slice_stride + idx, p1);
+                load_vec(a.y + (long long)(s + 2) * a.slice_stride + idx, p2);
+                load_vec(a.y + (long long)(s + 3) * a.slice_stride + idx, p3);
 #pragma unroll
-                for (int k = 0; k < VEC; ++k) br[k] += a.y[(long long)s * a.slice_stride + idx + k];
+                for (int k = 0; k < VEC; ++k) br[k] = (((br[k] + p0[k]) + p1[k]) + p2[k]) + p3[k];
+            }
+            for (; s < a.n_slices; ++s) {
+                float p0[VEC];
+                load_vec(a.y + (long long)s * a.slice_stride + idx, p0);
+#pragma unroll
+                for (int k = 0; k < VEC; ++k) br[k] += p0[k];
+            }
         } else {
             for (int j = 0; j < a.top; ++j) {
                 const int r = a.row_of[t * a.top + j];
                 if (r < 0) continue;
+                float p0[VEC];
+                load_vec(a.rows + (long long)r * a.d + c, p0);
 #pragma unroll
-                for (int k = 0; k < VEC; ++k) br[k] += a.rows[(long long)r * a.d + c + k];
+                for (int k = 0; k < VEC; ++k) br[k] += p0[k];
             }
         }
 #pragma unroll
         for (int k = 0; k < VEC; ++k) {
-            const float nb = a.b_gain != nullptr ? tanh_norm_one(br[k], a.b_alpha, a.b_gain[c + k], a.b_bias[c + k]) : br[k];
-            xv[k] = fmaf(a.mult, nb, xv[k]);
-            a.x[idx + k] = xv[k];
+            const float nbr = a.b_gain != nullptr ? tanh_norm_one<EXACT>(br[k], a.b_alpha, bg[k], bb[k]) : br[k];
+            xv[k] = fmaf(a.mult, nbr, xv[k]);
         }
+        store_vec(a.x + idx, xv);
     }
     if (a.n_gain != nullptr) {
+        float o[VEC];
 #pragma unroll
-        for (int k = 0; k < VEC; ++k)
-            out[idx + k] = from_float<TOut>(tanh_norm_one(xv[k], a.n_alpha, a.n_gain[c + k], a.n_bias[c + k]));
+        for (int k = 0; k < VEC; ++k) o[k] = tanh_norm_one<EXACT>(xv[k], a.n_alpha, ng[k], nb[k]);
+        store_vec(out + idx, o);
     }
 }
 
@@ -140,16 +184,23 @@ extern "C" int mlc_tanh_norm(float* x, const float* y, int n_slices, const float
     TanhNormArgs a{x, y, n_slices, (long long)n * d, rows, row_of, top, b_gain, b_bias, b_alpha, mult, n_gain, n_bias, n_alpha, d,
                    (long long)n * d};
     cudaStream_t s = (cudaStream_t)stream;
-    const bool vec = (d & 3) == 0;
+    // 16-byte accesses for rows whose length allows them, unless the step is so small that one entry a thread fills more SMs
+    const bool vec = (d & 3) == 0 && a.total >= (1 << 18) &&
+                     ((((uintptr_t)x) | ((uintptr_t)y) | ((uintptr_t)rows) | ((uintptr_t)b_gain) | ((uintptr_t)b_bias) |
+                       ((uintptr_t)n_gain) | ((uintptr_t)n_bias) | ((uintptr_t)out)) & 15) == 0;
     const long long items = vec ? a.total / 4 : a.total;
     const dim3 grid((unsigned)((items + 255) / 256)), block(256);
     cudaError_t e;
-    if (out_dtype == MLC_DTYPE_F32)
-        e = vec ? launch_pdl(tanh_norm_kernel<float, 4>, grid, block, 0, s, a, (float*)out)
-                : launch_pdl(tanh_norm_kernel<float, 1>, grid, block, 0, s, a, (float*)out);
-    else if (out_dtype == MLC_DTYPE_BF16)
-        e = vec ? launch_pdl(tanh_norm_kernel<bf16, 4>, grid, block, 0, s, a, (bf16*)out)
-                : launch_pdl(tanh_norm_kernel<bf16, 1>, grid, block, 0, s, a, (bf16*)out);
+    // a float32 output is the float32 engine: the library's tanh; 16 bits out: the fast form (see tanh_of)
+    if (out_dtype == MLC_DTYPE_F32 && n_gain != nullptr)
+        e = vec ? launch_pdl(tanh_norm_kernel<float, 4, true>, grid, block, 0, s, a, (float*)out)
+                : launch_pdl(tanh_norm_kernel<float, 1, true>, grid, block, 0, s, a, (float*)out);
+    else if (out_dtype == MLC_DTYPE_BF16 && n_gain != nullptr)
+        e = vec ? launch_pdl(tanh_norm_kernel<bf16, 4, false>, grid, block, 0, s, a, (bf16*)out)
+                : launch_pdl(tanh_norm_kernel<bf16, 1, false>, grid, block, 0, s, a, (bf16*)out);
+    else if (n_gain == nullptr)          // no output: the stream's update alone, with the library's tanh
+        e = vec ? launch_pdl(tanh_norm_kernel<float, 4, true>, grid, block, 0, s, a, (float*)nullptr)
+                : launch_pdl(tanh_norm_kernel<float, 1, true>, grid, block, 0, s, a, (float*)nullptr);
     else
         return MLC_ERR_BAD_DTYPE;
     return e == cudaSuccess ? 0 : (int)e;
